@@ -11,7 +11,8 @@ Groups.  A mixer declares its need (`KVNeed`: heads, head size, optional window;
 fixed shape per request).  Calls with the same KVNeed form one group with its own pool, sized for
 the same number of tokens.  A group with a window gives a page back as soon as every position in it
 lies before the window of the request's next token; its block-table entry becomes -1 and the
-attention kernels never look there.
+attention kernels never look there.  A group whose keys are visible inside a chunk of positions only
+does the same with the pages that lie wholly before the chunk of the request's next token.
 
 A request moves through reserve(n) -> (the step runs) -> commit(n).  `reserve` takes the pages the
 next n tokens need in every group, or nothing at all."""
@@ -30,6 +31,18 @@ class KVNeed:
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None  # None: all keys; n: the last n keys (the token itself included)
+    value_dim: Optional[int] = None  # size of a value row when it differs from the key's head_dim
+    key_rows: int = 1  # key rows per key/value head and token (a mixer with several score maps over the same values)
+    chunk: Optional[int] = None  # n: a token sees keys of its own chunk of n positions only (counted from position 0)
+
+    @property
+    def v_dim(self) -> int:
+        return self.head_dim if self.value_dim is None else self.value_dim
+
+    @property
+    def bounded(self) -> bool:
+        """True when keys far enough back are never read again, so that their pages can go back to the pool."""
+        return self.window is not None or self.chunk is not None
 
 
 @dataclass(frozen=True)
@@ -47,8 +60,10 @@ class CacheEntryRef:
 
 
 class KVGroup:
-    """All cache entries that share one KVNeed: one pool, one block table per request, and the
-    tensor kv[entry, 0 = keys | 1 = values, page, kv_head, slot_in_page, head_dim]."""
+    """All cache entries that share one KVNeed: one pool, one block table per request, and the tensors
+    k[entry, page, key row, slot_in_page, head_dim] and v[entry, page, kv_head, slot_in_page, value size].  Where
+    key and value rows have the same count and size (the usual case) both are halves of one tensor
+    kv[entry, 0 = keys | 1 = values, page, kv_head, slot_in_page, head_dim]."""
 
     def __init__(self, need: KVNeed, num_entries: int, num_pages: int, page_size: int):
         self.need = need
@@ -57,23 +72,39 @@ class KVGroup:
         self.pool = PagePool(num_pages)
         self.tables: Dict[Hashable, List[int]] = {}
         self.kv: Optional[torch.Tensor] = None
+        self.k: Optional[torch.Tensor] = None
+        self.v: Optional[torch.Tensor] = None
 
     def allocate_storage(self, dtype: torch.dtype, device) -> None:
         n = self.need
-        self.kv = torch.zeros(self.num_entries, 2, self.pool.num_pages, n.num_kv_heads, self.page_size,
-                              n.head_dim, dtype=dtype, device=device)
+        if n.key_rows == 1 and n.v_dim == n.head_dim:
+            self.kv = torch.zeros(self.num_entries, 2, self.pool.num_pages, n.num_kv_heads, self.page_size,
+                                  n.head_dim, dtype=dtype, device=device)
+            self.k, self.v = self.kv[:, 0], self.kv[:, 1]
+        else:
+            self.k = torch.zeros(self.num_entries, self.pool.num_pages, n.num_kv_heads * n.key_rows, self.page_size,
+                                 n.head_dim, dtype=dtype, device=device)
+            self.v = torch.zeros(self.num_entries, self.pool.num_pages, n.num_kv_heads, self.page_size, n.v_dim,
+                                 dtype=dtype, device=device)
+
+    def tensors(self):
+        """The storage as a list of tensors (for a caller that fills or inspects all of it)."""
+        return [self.kv] if self.kv is not None else [self.k, self.v]
 
     def bytes_per_token(self, itemsize: int) -> int:
-        return 2 * self.num_entries * self.need.num_kv_heads * self.need.head_dim * itemsize
+        n = self.need
+        return self.num_entries * n.num_kv_heads * (n.key_rows * n.head_dim + n.v_dim) * itemsize
 
     def pages_for(self, tokens: int) -> int:
         return -(-tokens // self.page_size)
 
     def first_needed_page(self, next_pos: int) -> int:
         """Index of the first page that the token at `next_pos` can still see."""
-        if self.need.window is None:
-            return 0
-        lowest_visible = max(0, next_pos - self.need.window + 1)
+        lowest_visible = 0
+        if self.need.window is not None:
+            lowest_visible = max(0, next_pos - self.need.window + 1)
+        if self.need.chunk is not None:
+            lowest_visible = max(lowest_visible, (next_pos // self.need.chunk) * self.need.chunk)
         return lowest_visible // self.page_size
 
 
@@ -220,7 +251,7 @@ class CacheManager:
         self._reserved[rid] = 0
         self.kv_len[rid] += n_new
         for g in self.groups:
-            if g.need.window is None:
+            if not g.need.bounded:
                 continue
             table = g.tables[rid]
             first = min(g.first_needed_page(self.kv_len[rid]), len(table))

@@ -33,8 +33,11 @@ def config_class_for(name: str) -> type:
 
 def config_from_dict(d: dict):
     archs = d.get("architectures")
+    if archs is None and isinstance(d.get("architecture"), str):   # some designs name themselves with one string
+        archs = [d["architecture"]]
     if not isinstance(archs, (list, tuple)) or not archs or not isinstance(archs[0], str):
-        raise ConfigError('config.json: key "architectures" must be a non-empty list of names')
+        raise ConfigError('config.json: key "architectures" must be a non-empty list of names '
+                          '(or "architecture" one name)')
     return config_class_for(archs[0]).from_dict(d)
 
 

@@ -19,7 +19,8 @@ class LayerSpec:
     """One layer: the parts it is made of and the kind of block that arranges them.
 
     `block` names an arrangement in the block registry.  The built-in "pre_norm" is
-    x += mixer(norm1(x)); x += ffn(norm2(x)); other arrangements (post-norm, both branches from one
+    x += mixer(norm1(x)); x += ffn(norm2(x)) (a layer without a feed-forward leaves `norm2` and `ffn` out);
+    other arrangements (post-norm, both branches from one
     normed input, norms on both sides of a part) are registered like parts and use the same fields,
     leaving out the ones they do not need and naming further parts in `more` as
     (role, family, PartSpec, weight name).  `prefix` is the weight-name prefix of the layer
@@ -35,6 +36,8 @@ class LayerSpec:
     norm2_name: str = "post_attention_layernorm"
     block: str = "pre_norm"
     more: Tuple[Tuple[str, str, PartSpec, str], ...] = ()
+    # what a branch's output is multiplied by before it joins the stream: x += residual_scale * mixer(norm1(x))
+    residual_scale: float = 1.0
 
 
 @dataclass(frozen=True)
@@ -42,9 +45,12 @@ class LayerCall:
     """One entry of the run order.  `layer` indexes `ModelSpec.layers` (a layer may be named
     twice).  Every call owns the cache entry with its own position in the order, unless
     `reads_cache_of` names an earlier call (by position in the order): then this call's mixer
-    writes nothing and reads that call's cache."""
+    writes nothing and reads that call's cache.  `add_embedding`: the embedding output (the stream as it was
+    before the first call) is added to the stream right before this call, as a model does that runs a span of
+    its layers several times and feeds the input in again at the start of every further pass."""
     layer: int
     reads_cache_of: Optional[int] = None
+    add_embedding: bool = False
 
 
 @dataclass(frozen=True)

@@ -1,8 +1,16 @@
-// Attention of the step's queries over the paged cache on the CUDA cores, any head size that is a
-// multiple of 16 up to 256, any number of heads and groups, any page size.  It is the attention of
-// the true 32-bit path and the fallback of the bfloat16 path.
+// Attention of the step's queries over the paged cache on the CUDA cores, any key size that is a
+// multiple of 8 and any value size up to 256 (the two may differ), any number of heads and groups, any
+// page size.  It is the attention of the true 32-bit path and the fallback of the bfloat16 path.
 //
-// The keys a query at position p sees are j in [max(0, p - window + 1), p].  They are walked in
+// Heads.  A query head has `maps` score maps, each an attention of its own over the same values: the
+// query rows of a token are laid out [head][map][kd], the key rows [key/value head][map][kd], the
+// value rows [key/value head][vd]; map m of query head h reads key row (h / group) * maps + m and
+// value row h / group, and the output rows are [head][map][vd].  maps = 1 is ordinary grouped-query
+// attention.  The output is of the cache's type or float32 (for a caller that combines the maps).
+//
+// The keys a query at position p sees are j in [lo, p] with lo = max(0, p - window + 1) when there is a
+// window and lo >= (p / chunk) * chunk when keys are visible inside a chunk of positions only (chunks
+// are counted from position 0 of the sequence).  They are walked in
 // tiles of 32 that start at multiples of 32 of the absolute position.  Tile number i (= j / 32) belongs
 // to lane i mod 8 of eight running softmaxes (m, l, o) in 32-bit, each of which takes its tiles in
 // ascending order; at the end the eight are merged in the order 0..7.  So the order of every sum is a
@@ -26,6 +34,17 @@ namespace tllm {
 
 constexpr int WARPS = 4;
 constexpr int MAX_HD = 256;
+
+// Where the rows of the cache lie and which keys are visible; `nq` and `nk` count (head, map) rows.
+struct Geometry {
+  int nq, nk, maps, kd, vd, page_size, window, chunk;
+  long long k_page_stride, k_head_stride, v_page_stride, v_head_stride;
+};
+__device__ __forceinline__ int lowest_key(const Geometry& g, int p) {
+  int lo = g.window > 0 ? max(0, p - g.window + 1) : 0;
+  if (g.chunk > 0) lo = max(lo, (p / g.chunk) * g.chunk);
+  return lo;
+}
 
 template <typename T> struct Vec;            // 16-byte vectors of the cache rows
 template <> struct Vec<float> { static constexpr int N = 4; };
@@ -56,8 +75,9 @@ struct Softmax {
 // One tile of 32 keys starting at j0 into the running softmax `st` (all lanes of the warp).
 template <typename T, int OD>
 __device__ __forceinline__ void attend_tile(Softmax<OD>& st, int j0, int lo, int p, const float* q_row, const T* kcache,
-                                            const T* vcache, const int* table, int max_blocks, int kvh, int hd,
-                                            int page_size, long long page_stride, long long head_stride, int lane) {
+                                            const T* vcache, const int* table, int max_blocks, int kh, int vh,
+                                            const Geometry& g, int lane) {
+  const int hd = g.kd, vd = g.vd, page_size = g.page_size;
   const int j = j0 + lane;
   bool valid = j >= lo && j <= p && j / page_size < max_blocks;
   const int page = valid ? table[j / page_size] : -1;
@@ -65,8 +85,8 @@ __device__ __forceinline__ void attend_tile(Softmax<OD>& st, int j0, int lo, int
   long long row_off = 0;
   float s = -CUDART_INF_F;
   if (valid) {
-    row_off = (long long)page * page_stride + (long long)kvh * head_stride + (long long)(j % page_size) * hd;
-    const T* krow = kcache + row_off;
+    row_off = (long long)page * g.v_page_stride + (long long)vh * g.v_head_stride + (long long)(j % page_size) * vd;
+    const T* krow = kcache + (long long)page * g.k_page_stride + (long long)kh * g.k_head_stride + (long long)(j % page_size) * hd;
     float acc = 0.f;
 #pragma unroll 4
     for (int d = 0; d < hd; d += Vec<T>::N) {
@@ -95,7 +115,7 @@ __device__ __forceinline__ void attend_tile(Softmax<OD>& st, int j0, int lo, int
 #pragma unroll
     for (int i = 0; i < OD; ++i) {
       const int d = lane + 32 * i;
-      if (d < hd) st.o[i] = fmaf(pk, to_f32(vrow[d]), st.o[i]);
+      if (d < vd) st.o[i] = fmaf(pk, to_f32(vrow[d]), st.o[i]);
     }
   }
 }
@@ -126,8 +146,9 @@ constexpr int GH = 4;
 template <typename T, int OD>
 __device__ __forceinline__ void attend_tile_grouped(Softmax<OD> (&st)[GH], int nh, int j0, int lo, int p,
                                                     const float (*q_rows)[OD * 32], const T* kcache, const T* vcache,
-                                                    const int* table, int max_blocks, int kvh, int hd, int page_size,
-                                                    long long page_stride, long long head_stride, int lane) {
+                                                    const int* table, int max_blocks, int kh, int vh,
+                                                    const Geometry& g, int lane) {
+  const int hd = g.kd, vd = g.vd, page_size = g.page_size;
   const int j = j0 + lane;
   bool valid = j >= lo && j <= p && j / page_size < max_blocks;
   const int page = valid ? table[j / page_size] : -1;
@@ -137,8 +158,8 @@ __device__ __forceinline__ void attend_tile_grouped(Softmax<OD> (&st)[GH], int n
 #pragma unroll
   for (int i = 0; i < GH; ++i) s[i] = -CUDART_INF_F;
   if (valid) {
-    row_off = (long long)page * page_stride + (long long)kvh * head_stride + (long long)(j % page_size) * hd;
-    const T* krow = kcache + row_off;
+    row_off = (long long)page * g.v_page_stride + (long long)vh * g.v_head_stride + (long long)(j % page_size) * vd;
+    const T* krow = kcache + (long long)page * g.k_page_stride + (long long)kh * g.k_head_stride + (long long)(j % page_size) * hd;
     float acc[GH];
 #pragma unroll
     for (int i = 0; i < GH; ++i) acc[i] = 0.f;
@@ -185,7 +206,7 @@ __device__ __forceinline__ void attend_tile_grouped(Softmax<OD> (&st)[GH], int n
 #pragma unroll
     for (int x = 0; x < OD; ++x) {
       const int d = lane + 32 * x;
-      if (d < hd) {
+      if (d < vd) {
         const float v = to_f32(vrow[d]);
 #pragma unroll
         for (int i = 0; i < GH; ++i)
@@ -195,39 +216,40 @@ __device__ __forceinline__ void attend_tile_grouped(Softmax<OD> (&st)[GH], int n
   }
 }
 
-// Many (token, head) pairs (prompts): one warp per (token, key/value head, up to GH of its query heads).  The eight
+// Many (token, head) pairs (prompts): one warp per (token, key row, up to GH of the query rows that read it).  The eight
 // softmaxes are walked one after the other (way w over its own tiles in ascending order, as everywhere), their results
 // parked in shared memory and merged per head in the order 0..7: the arithmetic of every head is that of the other two
 // launches, and the keys and values of a tile are fetched once for the heads of the group instead of once per head
 // (with one warp per pair the kernel was bound by those fetches: 34 GB through L2 per layer of a 2,048-token prompt).
 template <int OD> struct GroupedWarps { static constexpr int N = OD <= 2 ? 4 : (OD <= 4 ? 2 : 1); };
 
-template <typename T, int OD>
+template <typename T, typename TO, int OD>
 __global__ void __launch_bounds__(GroupedWarps<OD>::N * 32)
 paged_attention_grouped_kernel(const T* __restrict__ q, int q_row_stride, const T* __restrict__ kcache,
                                const T* __restrict__ vcache, const int* __restrict__ block_table,
                                int max_blocks, const int* __restrict__ token_request,
-                               const int* __restrict__ positions, T* __restrict__ out, int n_tokens,
-                               int nq, int nkv, int hd, int page_size, long long page_stride,
-                               long long head_stride, float scale, int window) {
+                               const int* __restrict__ positions, TO* __restrict__ out, int n_tokens,
+                               Geometry g, float scale) {
   constexpr int GW = GroupedWarps<OD>::N;
   __shared__ __align__(16) float q_s[GW][GH][OD * 32];
   __shared__ float way_s[GW][WAYS][GH][OD * 32 + 2];
   pdl_trigger();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int group = nq / nkv, chunks = (group + GH - 1) / GH;
+  const int nq = g.nq, nk = g.nk, hd = g.kd, vd = g.vd, maps = g.maps;
+  const int group = nq / nk, chunks = (group + GH - 1) / GH;
   const long long task = (long long)blockIdx.x * GW + warp;
-  if (task >= (long long)n_tokens * nkv * chunks) return;
-  const int t = (int)(task / (nkv * chunks)), rem = (int)(task % (nkv * chunks));
-  const int kvh = rem / chunks, h0 = (rem % chunks) * GH, nh = min(GH, group - h0);
-  const int head0 = kvh * group + h0;
+  if (task >= (long long)n_tokens * nk * chunks) return;
+  const int t = (int)(task / (nk * chunks)), rem = (int)(task % (nk * chunks));
+  const int kh = rem / chunks, h0 = (rem % chunks) * GH, nh = min(GH, group - h0);
+  const int kvh = kh / maps, map = kh % maps;   // query row of head h, map m: (h * maps + m)
+  const int vh = kvh;
   const int req = token_request[t];
   const int p = positions[t];
-  const int lo = window > 0 ? max(0, p - window + 1) : 0;
+  const int lo = lowest_key(g, p);
   const int* table = block_table + (size_t)req * max_blocks;
   for (int i = 0; i < nh; ++i) {
-    const T* qrow = q + (size_t)t * q_row_stride + (size_t)(head0 + i) * hd;
+    const T* qrow = q + (size_t)t * q_row_stride + (size_t)((kvh * group + h0 + i) * maps + map) * hd;
     for (int d = lane; d < hd; d += 32) q_s[warp][i][d] = to_f32(qrow[d]) * scale;
   }
   for (int i = nh; i < GH; ++i)
@@ -245,8 +267,7 @@ paged_attention_grouped_kernel(const T* __restrict__ q, int q_row_stride, const 
     }
     for (int j0 = first_group + w * 32; j0 <= p; j0 += 32 * WAYS)
       if (j0 + 31 >= lo)
-        attend_tile_grouped<T, OD>(st, nh, j0, lo, p, q_s[warp], kcache, vcache, table, max_blocks, kvh, hd, page_size,
-                                   page_stride, head_stride, lane);
+        attend_tile_grouped<T, OD>(st, nh, j0, lo, p, q_s[warp], kcache, vcache, table, max_blocks, kh, vh, g, lane);
 #pragma unroll
     for (int i = 0; i < GH; ++i) {
       if (lane == 0) { way_s[warp][w][i][OD * 32] = st[i].m; way_s[warp][w][i][OD * 32 + 1] = st[i].l; }
@@ -259,38 +280,39 @@ paged_attention_grouped_kernel(const T* __restrict__ q, int q_row_stride, const 
     float o[OD], l;
     merge_ways<OD>([&](int w) { return way_s[warp][w][i][OD * 32]; }, [&](int w) { return way_s[warp][w][i][OD * 32 + 1]; },
                    [&](int w, int x) { return way_s[warp][w][i][lane + 32 * x]; }, o, l);
-    T* orow = out + (size_t)t * nq * hd + (size_t)(head0 + i) * hd;
+    TO* orow = out + (size_t)t * nq * vd + (size_t)((kvh * group + h0 + i) * maps + map) * vd;
     const float inv = 1.f / l;
 #pragma unroll
     for (int x = 0; x < OD; ++x) {
       const int d = lane + 32 * x;
-      if (d < hd) orow[d] = from_f32<T>(o[x] * inv);
+      if (d < vd) orow[d] = from_f32<TO>(o[x] * inv);
     }
   }
 }
 
 // SPLIT = false: WARPS (token, head) pairs per CTA, one warp each, eight softmaxes in its registers.
 // SPLIT = true: one pair per CTA of eight warps, warp w carries softmax w.
-template <typename T, bool SPLIT, int OD>
+template <typename T, typename TO, bool SPLIT, int OD>
 __global__ void __launch_bounds__(SPLIT ? WAYS * 32 : WARPS * 32)
 paged_attention_generic_kernel(const T* __restrict__ q, int q_row_stride, const T* __restrict__ kcache,
                                const T* __restrict__ vcache, const int* __restrict__ block_table,
                                int max_blocks, const int* __restrict__ token_request,
-                               const int* __restrict__ positions, T* __restrict__ out, int n_tokens,
-                               int nq, int nkv, int hd, int page_size, long long page_stride,
-                               long long head_stride, float scale, int window) {
+                               const int* __restrict__ positions, TO* __restrict__ out, int n_tokens,
+                               Geometry g, float scale) {
   __shared__ __align__(16) float q_s[SPLIT ? 1 : WARPS][MAX_HD];
   __shared__ float merge_s[SPLIT ? WAYS : 1][SPLIT ? OD * 32 + 2 : 1];
   pdl_trigger();
   pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nq = g.nq, nk = g.nk, hd = g.kd, vd = g.vd, maps = g.maps;
   const long long task = SPLIT ? (long long)blockIdx.x : (long long)blockIdx.x * WARPS + warp;
   if (task >= (long long)n_tokens * nq) return;
-  const int t = (int)(task / nq), h = (int)(task % nq);
-  const int kvh = h / (nq / nkv);
+  const int t = (int)(task / nq), h = (int)(task % nq);   // h: the (head, map) row of the queries
+  const int vh = (h / maps) / (nq / nk);
+  const int kh = vh * maps + h % maps;
   const int req = token_request[t];
   const int p = positions[t];
-  const int lo = window > 0 ? max(0, p - window + 1) : 0;
+  const int lo = lowest_key(g, p);
   const int* table = block_table + (size_t)req * max_blocks;
 
   const T* qrow = q + (size_t)t * q_row_stride + (size_t)h * hd;
@@ -312,15 +334,15 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_row_stride, const 
     for (int i = 0; i < OD; ++i) st.o[i] = 0.f;
     for (int j0 = first_group + warp * 32; j0 <= p; j0 += 32 * WAYS)
       if (j0 + 31 >= lo)
-        attend_tile(st, j0, lo, p, q_row, kcache, vcache, table, max_blocks, kvh, hd, page_size, page_stride, head_stride, lane);
+        attend_tile(st, j0, lo, p, q_row, kcache, vcache, table, max_blocks, kh, vh, g, lane);
     if (lane == 0) { merge_s[warp][OD * 32] = st.m; merge_s[warp][OD * 32 + 1] = st.l; }
 #pragma unroll
     for (int i = 0; i < OD; ++i)
-      if (lane + 32 * i < hd) merge_s[warp][lane + 32 * i] = st.o[i];
+      if (lane + 32 * i < vd) merge_s[warp][lane + 32 * i] = st.o[i];
     __syncthreads();
     if (warp != 0) return;
     merge_ways<OD>([&](int w) { return merge_s[w][OD * 32]; }, [&](int w) { return merge_s[w][OD * 32 + 1]; },
-               [&](int w, int i) { return lane + 32 * i < hd ? merge_s[w][lane + 32 * i] : 0.f; }, o, l);
+               [&](int w, int i) { return lane + 32 * i < vd ? merge_s[w][lane + 32 * i] : 0.f; }, o, l);
   } else {
     Softmax<OD> st[WAYS];
 #pragma unroll
@@ -334,86 +356,108 @@ paged_attention_generic_kernel(const T* __restrict__ q, int q_row_stride, const 
       for (int w = 0; w < WAYS; ++w) {
         const int j0 = g0 + w * 32;
         if (j0 <= p && j0 + 31 >= lo)
-          attend_tile(st[w], j0, lo, p, q_row, kcache, vcache, table, max_blocks, kvh, hd, page_size, page_stride, head_stride, lane);
+          attend_tile(st[w], j0, lo, p, q_row, kcache, vcache, table, max_blocks, kh, vh, g, lane);
       }
     }
     merge_ways<OD>([&](int w) { return st[w].m; }, [&](int w) { return st[w].l; }, [&](int w, int i) { return st[w].o[i]; }, o, l);
   }
-  T* orow = out + (size_t)t * nq * hd + (size_t)h * hd;
+  TO* orow = out + (size_t)t * nq * vd + (size_t)h * vd;
   const float inv = 1.f / l;
 #pragma unroll
   for (int i = 0; i < OD; ++i) {
     const int d = lane + 32 * i;
-    if (d < hd) orow[d] = from_f32<T>(o[i] * inv);
+    if (d < vd) orow[d] = from_f32<TO>(o[i] * inv);
   }
+}
+
+template <typename T, typename TO>
+static int launch_attention(const void* q, int q_row_stride, const void* kcache, const void* vcache, const int* block_table,
+                            int max_blocks, const int* token_request, const int* positions, void* out, int n_tokens,
+                            const Geometry& g, float scale, bool split, bool grouped, int od, long long blocks,
+                            cudaStream_t s) {
+#define TLLM_ATT_GENERIC(SPLIT_, OD_)                                                                                  \
+  TLLM_LAUNCH("paged_attention_generic", (paged_attention_generic_kernel<T, TO, SPLIT_, OD_>), (unsigned)blocks,       \
+              (SPLIT_ ? WAYS : WARPS) * 32, 0, s, (const T*)q, q_row_stride, (const T*)kcache, (const T*)vcache,       \
+              block_table, max_blocks, token_request, positions, (TO*)out, n_tokens, g, scale)
+#define TLLM_ATT_GROUPED(OD_)                                                                                          \
+  TLLM_LAUNCH("paged_attention_grouped", (paged_attention_grouped_kernel<T, TO, OD_>), (unsigned)blocks,               \
+              GroupedWarps<OD_>::N * 32, 0, s, (const T*)q, q_row_stride, (const T*)kcache, (const T*)vcache,          \
+              block_table, max_blocks, token_request, positions, (TO*)out, n_tokens, g, scale)
+  if (split) {
+    if (od == 2) TLLM_ATT_GENERIC(true, 2); else if (od == 4) TLLM_ATT_GENERIC(true, 4); else TLLM_ATT_GENERIC(true, 8);
+  } else if (grouped) {
+    if (od == 2) TLLM_ATT_GROUPED(2); else if (od == 4) TLLM_ATT_GROUPED(4); else TLLM_ATT_GROUPED(8);
+  } else {
+    if (od == 2) TLLM_ATT_GENERIC(false, 2); else if (od == 4) TLLM_ATT_GENERIC(false, 4); else TLLM_ATT_GENERIC(false, 8);
+  }
+#undef TLLM_ATT_GROUPED
+#undef TLLM_ATT_GENERIC
+  return TLLM_OK;
 }
 
 }  // namespace tllm
 
 using namespace tllm;
 
+// Attention with `maps` score maps per head and key rows of `kd`, value rows of `vd` values.  `nq` query heads and
+// `nkv` key/value heads; the key cache holds nkv * maps rows per slot, the value cache nkv.  `chunk` > 0: keys are
+// visible inside the query's chunk of positions only.  out_f32 != 0: the output rows are float32 whatever the cache's type.
+extern "C" int tllm_paged_attention_maps(const void* q, int q_row_stride, const void* kcache, const void* vcache,
+                                         const int* block_table, int max_blocks, const int* token_request,
+                                         const int* positions, void* out, int n_tokens, int nq, int nkv, int maps, int kd,
+                                         int vd, int page_size, long long k_page_stride, long long k_head_stride,
+                                         long long v_page_stride, long long v_head_stride, float scale, int window,
+                                         int chunk, int dtype, int out_f32, int split_override, void* stream) {
+  TLLM_REQUIRE(n_tokens > 0 && nq > 0 && nkv > 0 && nq % nkv == 0 && maps > 0,
+               "attention: %d tokens, %d heads, %d key/value heads (heads must be a multiple of key/value heads)", n_tokens, nq, nkv);
+  TLLM_REQUIRE(kd >= 8 && kd <= MAX_HD && kd % 8 == 0 && vd >= 1 && vd <= MAX_HD,
+               "attention: key size %d / value size %d is not built (keys: multiples of 8 up to %d, values: up to %d)", kd, vd, MAX_HD, MAX_HD);
+  TLLM_REQUIRE(page_size > 0 && max_blocks > 0 && window >= 0 && chunk >= 0, "attention: page size %d, %d blocks, window %d, chunk %d", page_size, max_blocks, window, chunk);
+  const int elem = dtype == TLLM_F32 ? 4 : 2;
+  TLLM_REQUIRE(dtype == TLLM_F32 || dtype == TLLM_BF16, "attention: unknown dtype code %d", dtype);
+  TLLM_REQUIRE(((size_t)kcache % 16) == 0 && (k_page_stride * elem) % 16 == 0 && (k_head_stride * elem) % 16 == 0,
+               "attention: key rows must be 16-byte aligned");
+  Geometry g;
+  g.nq = nq * maps; g.nk = nkv * maps; g.maps = maps; g.kd = kd; g.vd = vd; g.page_size = page_size; g.window = window;
+  g.chunk = chunk; g.k_page_stride = k_page_stride; g.k_head_stride = k_head_stride; g.v_page_stride = v_page_stride;
+  g.v_head_stride = v_head_stride;
+  const long long tasks = (long long)n_tokens * g.nq;
+  // few pairs (decoded tokens): eight warps per pair; the result is the same to the bit
+  int dev = 0, sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+    TLLM_FAIL(TLLM_ERR_CUDA, "attention: cannot read the number of SMs");
+  // split_override: -1 by the number of pairs; 1 eight warps per pair; 0 one warp per (token, key row, four query rows);
+  // 2 one warp per pair (the plainest form, kept for comparison: all give the same bits)
+  const bool split = split_override >= 0 ? split_override == 1 : tasks <= 8LL * sms;
+  const bool grouped = !split && split_override != 2;
+  const int hd = kd > vd ? kd : vd;
+  const int od = hd <= 64 ? 2 : (hd <= 128 ? 4 : 8);
+  const int gw = od <= 2 ? 4 : (od <= 4 ? 2 : 1);
+  const long long gtasks = (long long)n_tokens * g.nk * ((nq / nkv + GH - 1) / GH);
+  const long long blocks = split ? tasks : (grouped ? (gtasks + gw - 1) / gw : (tasks + WARPS - 1) / WARPS);
+  TLLM_REQUIRE(blocks <= 2147483647LL, "attention: %lld (token, head) pairs exceed the grid", tasks);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == TLLM_F32)
+    return launch_attention<float, float>(q, q_row_stride, kcache, vcache, block_table, max_blocks, token_request, positions, out,
+                                          n_tokens, g, scale, split, grouped, od, blocks, s);
+  if (out_f32)
+    return launch_attention<__nv_bfloat16, float>(q, q_row_stride, kcache, vcache, block_table, max_blocks, token_request,
+                                                  positions, out, n_tokens, g, scale, split, grouped, od, blocks, s);
+  return launch_attention<__nv_bfloat16, __nv_bfloat16>(q, q_row_stride, kcache, vcache, block_table, max_blocks, token_request,
+                                                        positions, out, n_tokens, g, scale, split, grouped, od, blocks, s);
+}
+
 extern "C" int tllm_paged_attention_generic(const void* q, int q_row_stride, const void* kcache, const void* vcache,
                                             const int* block_table, int max_blocks, const int* token_request,
                                             const int* positions, void* out, int n_tokens, int nq, int nkv, int hd,
                                             int page_size, long long page_stride, long long head_stride,
                                             float scale, int window, int dtype, int split_override, void* stream) {
-  TLLM_REQUIRE(n_tokens > 0 && nq > 0 && nkv > 0 && nq % nkv == 0,
-               "attention: %d tokens, %d heads, %d key/value heads (heads must be a multiple of key/value heads)", n_tokens, nq, nkv);
   TLLM_REQUIRE(hd >= 16 && hd <= MAX_HD && hd % 16 == 0,
                "attention: head size %d is not built (multiples of 16 up to %d are)", hd, MAX_HD);
-  TLLM_REQUIRE(page_size > 0 && max_blocks > 0 && window >= 0, "attention: page size %d, %d blocks, window %d", page_size, max_blocks, window);
   const int elem = dtype == TLLM_F32 ? 4 : 2;
-  TLLM_REQUIRE(((size_t)kcache % 16) == 0 && ((size_t)vcache % 16) == 0 && (page_stride * elem) % 16 == 0 && (head_stride * elem) % 16 == 0,
+  TLLM_REQUIRE(((size_t)vcache % 16) == 0 && (page_stride * elem) % 16 == 0 && (head_stride * elem) % 16 == 0,
                "attention: cache rows must be 16-byte aligned");
-  const long long tasks = (long long)n_tokens * nq;
-  // few pairs (decoded tokens): eight warps per pair; the result is the same to the bit
-  int dev = 0, sms = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
-    TLLM_FAIL(TLLM_ERR_CUDA, "attention: cannot read the number of SMs");
-  // split_override: -1 by the number of pairs; 1 eight warps per pair; 0 one warp per (token, key/value head, four heads);
-  // 2 one warp per pair (the plainest form, kept for comparison: all give the same bits)
-  const bool split = split_override >= 0 ? split_override == 1 : tasks <= 8LL * sms;
-  const bool grouped = !split && split_override != 2;
-  const int od = hd <= 64 ? 2 : (hd <= 128 ? 4 : 8);
-  const int gw = od <= 2 ? 4 : (od <= 4 ? 2 : 1);
-  const long long gtasks = (long long)n_tokens * nkv * ((nq / nkv + GH - 1) / GH);
-  const long long blocks = split ? tasks : (grouped ? (gtasks + gw - 1) / gw : (tasks + WARPS - 1) / WARPS);
-  TLLM_REQUIRE(blocks <= 2147483647LL, "attention: %lld (token, head) pairs exceed the grid", tasks);
-  cudaStream_t s = (cudaStream_t)stream;
-#define TLLM_ATT_GENERIC(T_, SPLIT_, OD_)                                                                             \
-  TLLM_LAUNCH("paged_attention_generic", (paged_attention_generic_kernel<T_, SPLIT_, OD_>), (unsigned)blocks,          \
-              (SPLIT_ ? WAYS : WARPS) * 32, 0, s, (const T_*)q, q_row_stride, (const T_*)kcache, (const T_*)vcache,    \
-              block_table, max_blocks, token_request, positions, (T_*)out, n_tokens, nq, nkv, hd, page_size,           \
-              page_stride, head_stride, scale, window)
-#define TLLM_ATT_GENERIC_HD(T_, SPLIT_)                              \
-  do {                                                              \
-    if (hd <= 64) TLLM_ATT_GENERIC(T_, SPLIT_, 2);                   \
-    else if (hd <= 128) TLLM_ATT_GENERIC(T_, SPLIT_, 4);             \
-    else TLLM_ATT_GENERIC(T_, SPLIT_, 8);                            \
-  } while (0)
-#define TLLM_ATT_GROUPED(T_, OD_)                                                                                     \
-  TLLM_LAUNCH("paged_attention_grouped", (paged_attention_grouped_kernel<T_, OD_>), (unsigned)blocks,                  \
-              GroupedWarps<OD_>::N * 32, 0, s, (const T_*)q, q_row_stride, (const T_*)kcache, (const T_*)vcache,      \
-              block_table, max_blocks, token_request, positions, (T_*)out, n_tokens, nq, nkv, hd, page_size,           \
-              page_stride, head_stride, scale, window)
-#define TLLM_ATT_GROUPED_HD(T_)                          \
-  do {                                                  \
-    if (od == 2) TLLM_ATT_GROUPED(T_, 2);                \
-    else if (od == 4) TLLM_ATT_GROUPED(T_, 4);           \
-    else TLLM_ATT_GROUPED(T_, 8);                        \
-  } while (0)
-  if (dtype == TLLM_F32) {
-    if (split) TLLM_ATT_GENERIC_HD(float, true); else if (grouped) TLLM_ATT_GROUPED_HD(float); else TLLM_ATT_GENERIC_HD(float, false);
-  } else if (dtype == TLLM_BF16) {
-    if (split) TLLM_ATT_GENERIC_HD(__nv_bfloat16, true);
-    else if (grouped) TLLM_ATT_GROUPED_HD(__nv_bfloat16);
-    else TLLM_ATT_GENERIC_HD(__nv_bfloat16, false);
-  } else {
-    TLLM_FAIL(TLLM_ERR_ARG, "attention: unknown dtype code %d", dtype);
-  }
-#undef TLLM_ATT_GENERIC_HD
-#undef TLLM_ATT_GROUPED_HD
-#undef TLLM_ATT_GROUPED
-#undef TLLM_ATT_GENERIC
-  return TLLM_OK;
+  return tllm_paged_attention_maps(q, q_row_stride, kcache, vcache, block_table, max_blocks, token_request, positions, out,
+                                   n_tokens, nq, nkv, 1, hd, hd, page_size, page_stride, head_stride, page_stride, head_stride,
+                                   scale, window, 0, dtype, 0, split_override, stream);
 }

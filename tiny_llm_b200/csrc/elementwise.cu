@@ -272,9 +272,197 @@ __global__ void rope_kv_write_vec_kernel(T* __restrict__ qkv, float* __restrict_
   }
 }
 
+
+// ---------------------------------------------------------------- embedding added into the stream: out[t,:] += table[tokens[t],:]
+// (a model that runs a span of layers several times adds the embedding output again before each further pass)
+template <typename T>
+__global__ void embedding_add_kernel(const int* __restrict__ tokens, const T* __restrict__ table,
+                                     float* __restrict__ out, int n_tokens, int hidden) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  if (t >= n_tokens) return;
+  const T* row = table + (size_t)tokens[t] * hidden;
+  float* dst = out + (size_t)t * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] += to_f32(row[i]);
+}
+
+// ---------------------------------------------------------------- Dynamic Tanh
+// y_j = tanh(alpha x_j) w_j + b_j: a norm without statistics; alpha is one number of the model, read from the device.
+template <typename T>
+__global__ void dyt_norm_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b,
+                                const float* __restrict__ alpha, T* __restrict__ out, const int* __restrict__ rows,
+                                int n_rows, int hidden) {
+  pdl_trigger();
+  const float a = __ldg(alpha);
+  const int r = blockIdx.x;
+  const int src_row = r < n_rows ? (rows ? rows[r] : r) : 0;
+  pdl_wait();
+  if (r >= n_rows) return;
+  const float* src = x + (size_t)src_row * hidden;
+  T* dst = out + (size_t)r * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = from_f32<T>(fmaf(tanhf(a * src[i]), w[i], b[i]));
+}
+
+// ---------------------------------------------------------------- rotate pairs and cache
+// qkv row: [nq*kd queries | nk*kd keys | nv*vd values]; nq and nk count rows of kd values (heads times score maps).
+// The first rot_dims values of every query and key row are rotated, value 2i with value 2i+1, by the angle
+// pos * freq[i] (angle, cosine and sine in 32-bit); the rest pass unchanged.  Queries are rewritten in place; keys go
+// to the key pages (rows of kd values, nk per slot), values to the value pages (rows of vd values, nv per slot).
+template <typename T>
+__global__ void rope_pairs_kv_write_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
+                                           const float* __restrict__ freq, int rot_dims, int n_tokens, int nq, int nk,
+                                           int nv, int kd, int vd, int row_stride, T* __restrict__ kcache,
+                                           T* __restrict__ vcache, const int* __restrict__ slot_mapping, int page_size,
+                                           long long k_page_stride, long long k_head_stride, long long v_page_stride,
+                                           long long v_head_stride) {
+  __shared__ float cs[256], sn[256];   // rot_dims / 2 <= 256
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  if (t >= n_tokens) return;
+  const float pos = (float)positions[t];
+  const int half_rot = rot_dims / 2, half_kd = kd / 2;
+  for (int i = threadIdx.x; i < half_rot; i += blockDim.x) {
+    const float ang = __fmul_rn(pos, freq[i]);
+    cs[i] = cosf(ang);
+    sn[i] = sinf(ang);
+  }
+  __syncthreads();
+  T* row = qkv + (size_t)t * row_stride;
+  const int slot = slot_mapping[t];
+  if (slot < 0) return;   // a token without a slot writes nothing
+  const long long page = slot / page_size, off = slot % page_size;
+  T* kbase = kcache + page * k_page_stride + off * kd;
+  T* vbase = vcache + page * v_page_stride + off * vd;
+  for (int idx = threadIdx.x; idx < (nq + nk) * half_kd; idx += blockDim.x) {
+    const int h = idx / half_kd, i = idx % half_kd;
+    const T* srcp = row + (size_t)h * kd + 2 * i;
+    const float u = to_f32(srcp[0]), v = to_f32(srcp[1]);
+    float ou = u, ov = v;
+    if (i < half_rot) {
+      const float c = cs[i], s = sn[i];
+      ou = fmaf(u, c, -__fmul_rn(v, s));
+      ov = fmaf(v, c, __fmul_rn(u, s));
+    }
+    T* dst = h < nq ? row + (size_t)h * kd + 2 * i : kbase + (long long)(h - nq) * k_head_stride + 2 * i;
+    dst[0] = from_f32<T>(ou);
+    dst[1] = from_f32<T>(ov);
+  }
+  const T* vsrc = row + (size_t)(nq + nk) * kd;
+  for (int idx = threadIdx.x; idx < nv * vd; idx += blockDim.x) {
+    const int h = idx / vd, i = idx % vd;
+    vbase[(long long)h * v_head_stride + i] = vsrc[idx];
+  }
+}
+
+// ---------------------------------------------------------------- differential combine
+// a: float32 [T, heads, 2, vd], the outputs of a head's two score maps over the same values.
+// lambda = exp(sum(lq1 lk1)) - exp(sum(lq2 lk2)) + diff (one number of the layer, recomputed by every warp in the same
+// order); o = a1 - lambda a2; out = o / sqrt(mean(o^2) + eps) * (1 - diff).  One warp per (token, head); vd <= 256.
+template <typename T>
+__global__ void diff_combine_kernel(const float* __restrict__ a, const float* __restrict__ lq1, const float* __restrict__ lk1,
+                                    const float* __restrict__ lq2, const float* __restrict__ lk2, int kd, float diff,
+                                    float eps, T* __restrict__ out, long long n_rows, int vd) {
+  pdl_trigger();
+  const int lane = threadIdx.x & 31;
+  float s1 = 0.f, s2 = 0.f;
+  for (int i = lane; i < kd; i += 32) { s1 = fmaf(lq1[i], lk1[i], s1); s2 = fmaf(lq2[i], lk2[i], s2); }
+  s1 = warp_sum(s1); s2 = warp_sum(s2);
+  const float lambda = expf(s1) - expf(s2) + diff;
+  pdl_wait();
+  const long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= n_rows) return;
+  const float* a1 = a + r * 2 * vd;
+  const float* a2 = a1 + vd;
+  float o[8];
+  float ss = 0.f;
+#pragma unroll
+  for (int x = 0; x < 8; ++x) {
+    const int d = lane + 32 * x;
+    o[x] = d < vd ? fmaf(-lambda, a2[d], a1[d]) : 0.f;
+    ss = fmaf(o[x], o[x], ss);
+  }
+  ss = warp_sum(ss);
+  const float inv = (1.f - diff) / sqrtf(ss / (float)vd + eps);
+  T* dst = out + r * vd;
+#pragma unroll
+  for (int x = 0; x < 8; ++x) {
+    const int d = lane + 32 * x;
+    if (d < vd) dst[d] = from_f32<T>(o[x] * inv);
+  }
+}
+
 }  // namespace tllm
 
 using namespace tllm;
+
+extern "C" int tllm_embedding_add(const int* tokens, const void* table, float* out, int n_tokens, int hidden,
+                                  int dtype, void* stream) {
+  TLLM_REQUIRE(n_tokens > 0 && hidden > 0, "embedding_add: empty input (%d tokens, width %d)", n_tokens, hidden);
+  const int threads = hidden >= 1024 ? 256 : 128;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == TLLM_F32)
+    TLLM_LAUNCH("embedding_add", embedding_add_kernel<float>, n_tokens, threads, 0, s, tokens, (const float*)table, out, n_tokens, hidden);
+  else if (dtype == TLLM_BF16)
+    TLLM_LAUNCH("embedding_add", embedding_add_kernel<__nv_bfloat16>, n_tokens, threads, 0, s, tokens, (const __nv_bfloat16*)table, out, n_tokens, hidden);
+  else
+    TLLM_FAIL(TLLM_ERR_ARG, "embedding_add: unknown dtype code %d", dtype);
+  return TLLM_OK;
+}
+
+extern "C" int tllm_dyt_norm(const float* x, const float* w, const float* b, const float* alpha, void* out, const int* rows,
+                             int n_rows, int hidden, int out_dtype, void* stream) {
+  TLLM_REQUIRE(n_rows > 0 && hidden > 0, "dyt_norm: empty input (%d rows, width %d)", n_rows, hidden);
+  const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (out_dtype == TLLM_F32)
+    TLLM_LAUNCH("dyt_norm", dyt_norm_kernel<float>, n_rows, threads, 0, s, x, w, b, alpha, (float*)out, rows, n_rows, hidden);
+  else if (out_dtype == TLLM_BF16)
+    TLLM_LAUNCH("dyt_norm", dyt_norm_kernel<__nv_bfloat16>, n_rows, threads, 0, s, x, w, b, alpha, (__nv_bfloat16*)out, rows, n_rows, hidden);
+  else
+    TLLM_FAIL(TLLM_ERR_ARG, "dyt_norm: unknown dtype code %d", out_dtype);
+  return TLLM_OK;
+}
+
+extern "C" int tllm_rope_pairs_kv_write(void* qkv, const int* positions, const float* freq, int rot_dims, int n_tokens,
+                                        int nq, int nk, int nv, int kd, int vd, int row_stride, void* kcache, void* vcache,
+                                        const int* slot_mapping, int page_size, long long k_page_stride,
+                                        long long k_head_stride, long long v_page_stride, long long v_head_stride,
+                                        int dtype, void* stream) {
+  TLLM_REQUIRE(n_tokens > 0 && nq > 0 && nk > 0 && nv > 0 && vd > 0, "rope_pairs_kv_write: empty input");
+  TLLM_REQUIRE(kd > 0 && kd % 2 == 0, "rope_pairs_kv_write: key size %d must be even", kd);
+  TLLM_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= kd && rot_dims <= 512 && (rot_dims == 0 || freq),
+               "rope_pairs_kv_write: %d rotated values of %d (even, at most the key size and 512, with a frequency table)", rot_dims, kd);
+  TLLM_REQUIRE(kcache && vcache && slot_mapping && page_size > 0, "rope_pairs_kv_write: needs cache pointers, a slot mapping and a page size");
+  const int work = (nq + nk) * kd / 2;
+  const int threads = work >= 512 ? 256 : 128;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == TLLM_F32)
+    TLLM_LAUNCH("rope_pairs_kv_write", rope_pairs_kv_write_kernel<float>, n_tokens, threads, 0, s, (float*)qkv, positions, freq, rot_dims, n_tokens, nq, nk, nv, kd, vd, row_stride, (float*)kcache, (float*)vcache, slot_mapping, page_size, k_page_stride, k_head_stride, v_page_stride, v_head_stride);
+  else if (dtype == TLLM_BF16)
+    TLLM_LAUNCH("rope_pairs_kv_write", rope_pairs_kv_write_kernel<__nv_bfloat16>, n_tokens, threads, 0, s, (__nv_bfloat16*)qkv, positions, freq, rot_dims, n_tokens, nq, nk, nv, kd, vd, row_stride, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, slot_mapping, page_size, k_page_stride, k_head_stride, v_page_stride, v_head_stride);
+  else
+    TLLM_FAIL(TLLM_ERR_ARG, "rope_pairs_kv_write: unknown dtype code %d", dtype);
+  return TLLM_OK;
+}
+
+extern "C" int tllm_diff_combine(const float* a, const float* lq1, const float* lk1, const float* lq2, const float* lk2,
+                                 int kd, float diff, float eps, void* out, long long n_rows, int vd, int out_dtype,
+                                 void* stream) {
+  TLLM_REQUIRE(n_rows > 0 && vd > 0 && vd <= 256 && kd > 0, "diff_combine: %lld rows of %d values (at most 256), key size %d", n_rows, vd, kd);
+  const int warps = 4;
+  const long long blocks = (n_rows + warps - 1) / warps;
+  TLLM_REQUIRE(blocks <= 2147483647LL, "diff_combine: %lld rows exceed the grid", n_rows);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (out_dtype == TLLM_F32)
+    TLLM_LAUNCH("diff_combine", diff_combine_kernel<float>, (unsigned)blocks, warps * 32, 0, s, a, lq1, lk1, lq2, lk2, kd, diff, eps, (float*)out, n_rows, vd);
+  else if (out_dtype == TLLM_BF16)
+    TLLM_LAUNCH("diff_combine", diff_combine_kernel<__nv_bfloat16>, (unsigned)blocks, warps * 32, 0, s, a, lq1, lk1, lq2, lk2, kd, diff, eps, (__nv_bfloat16*)out, n_rows, vd);
+  else
+    TLLM_FAIL(TLLM_ERR_ARG, "diff_combine: unknown dtype code %d", out_dtype);
+  return TLLM_OK;
+}
 
 extern "C" int tllm_embedding(const int* tokens, const void* table, float* out, int n_tokens, int hidden,
                               int dtype, void* stream) {

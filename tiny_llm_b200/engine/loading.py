@@ -34,11 +34,15 @@ def load_model(model_dir: str, dtype, device="cuda:0"):
 
 
 def make_runner(model: DecoderModel, dtype, device="cuda:0", max_tokens: int = 8192, page_size: int = 16,
-                max_requests: int = 64, max_tokens_per_step: Optional[int] = None) -> ModelRunner:
-    """`max_tokens` sizes every cache group's pool (rounded up to whole pages)."""
+                max_requests: int = 64, max_tokens_per_step: Optional[int] = None,
+                max_positions: Optional[int] = None) -> ModelRunner:
+    """`max_tokens` sizes every cache group's pool (rounded up to whole pages); `max_positions` caps the length of
+    a request below the model's own limit (it sizes the block tables of the step's metadata)."""
     dtype = parse_dtype(dtype)
+    if max_positions is None:   # no request outgrows the pool unless the caller says so
+        max_positions = min(model.spec.max_positions, max(max_tokens, page_size))
     cache = CacheManager(model.cache_needs(), max_tokens=max_tokens, page_size=page_size, max_slots=max_requests)
     cache.allocate_storage(dtype, device)
     return ModelRunner(model, cache, dtype, device,
                        max_tokens_per_step=max_tokens_per_step or min(max_tokens, 8192),
-                       max_requests_per_step=max_requests)
+                       max_requests_per_step=max_requests, max_positions=max_positions)

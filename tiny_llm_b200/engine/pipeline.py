@@ -27,9 +27,10 @@ class _Pending:
 class Pipeline:
     def __init__(self, model_path: str, dtype="bfloat16", device: int = 0, page_size: int = 16,
                  max_tokens: Optional[int] = None, max_requests: int = 64, max_tokens_per_step: int = 2048,
-                 chunk: Optional[int] = None):
+                 chunk: Optional[int] = None, max_positions: Optional[int] = None):
         """`max_tokens`: tokens the cache pool holds (default: max_requests x the model's positions,
-        capped at 1M tokens).  `chunk`: the largest portion of one prompt in one step (default: the step's whole
+        capped at 1M tokens).  `max_positions`: the longest request (default: the model's own limit, or what the
+        pool holds if that is less).  `chunk`: the largest portion of one prompt in one step (default: the step's whole
         token budget; measured at the TinyLlama sizes a step of 512 prompt tokens runs at 233,000 tokens a second and a
         step of 2,048 at 448,000, so a prompt is cut no finer than the budget asks)."""
         if not chunk:
@@ -46,9 +47,11 @@ class Pipeline:
         spec = self.model.spec
         if max_tokens is None:
             max_tokens = min(max_requests * spec.max_positions, 1 << 20)
+        positions = min(spec.max_positions, max_positions or max_tokens)
         self.runner = make_runner(self.model, self.dtype, self.device, max_tokens=max_tokens, page_size=page_size,
-                                  max_requests=max_requests, max_tokens_per_step=max_tokens_per_step)
-        self.scheduler = Scheduler(self.runner.cache, spec.max_positions, max_tokens_per_step=max_tokens_per_step,
+                                  max_requests=max_requests, max_tokens_per_step=max_tokens_per_step,
+                                  max_positions=positions)
+        self.scheduler = Scheduler(self.runner.cache, positions, max_tokens_per_step=max_tokens_per_step,
                                    max_requests_per_step=max_requests, chunk=chunk,
                                    eos_token_ids=spec.eos_token_ids)
         self.sampler = Sampler(self.device, spec.vocab_size, max_rows=max(2, max_requests + max_requests % 2))

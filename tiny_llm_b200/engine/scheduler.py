@@ -99,7 +99,8 @@ class Scheduler:
             # the fewest tokens the request must be able to hold pages for: all of them, or, in a group
             # with a window, the window and the token being written, rounded out to whole pages at both
             # ends (pages behind the window come back only after the step that passed them)
-            most = total if g.need.window is None else min(total, g.need.window + 2 * g.page_size)
+            reach = min(x for x in (g.need.window, g.need.chunk, total) if x is not None)
+            most = total if not g.need.bounded else min(total, reach + 2 * g.page_size)
             if g.pages_for(most) > g.pool.num_pages:
                 raise RequestRefused(f"request {request.rid!r}: {most} tokens need {g.pages_for(most)} pages, "
                                      f"the pool has {g.pool.num_pages}")

@@ -41,8 +41,8 @@ class StepEntry:
 @dataclass
 class KVView:
     """What a mixer with a KVNeed gets: its entry's pages and the step's tables of its group."""
-    k: torch.Tensor              # [pages, kv_heads, page_size, head_dim]
-    v: torch.Tensor
+    k: torch.Tensor              # [pages, key rows, page_size, head_dim]
+    v: torch.Tensor              # [pages, kv_heads, page_size, value size]
     block_table: torch.Tensor    # int32 [R, max_blocks], -1 where a page was given back
     slot_mapping: torch.Tensor   # int32 [T]: page * page_size + offset of every token of the step
     page_size: int
@@ -96,7 +96,7 @@ class StepContext:
         if ref.group is not None:
             g = self.runner.cache.groups[ref.group]
             m = self.batch.groups[ref.group]
-            return KVView(g.kv[ref.entry, 0], g.kv[ref.entry, 1], m.block_table, m.slot_mapping, g.page_size)
+            return KVView(g.k[ref.entry], g.v[ref.entry], m.block_table, m.slot_mapping, g.page_size)
         if ref.state is not None:
             return StateView(self.runner.cache.slots.tensors[ref.state])
         return None
@@ -106,7 +106,8 @@ class ModelRunner:
     """Owns the model's device side: weights, cache storage, workspace, and the step function."""
 
     def __init__(self, model, cache: CacheManager, dtype: torch.dtype, device,
-                 max_tokens_per_step: int = 8192, max_requests_per_step: int = 256):
+                 max_tokens_per_step: int = 8192, max_requests_per_step: int = 256,
+                 max_positions: Optional[int] = None):
         if not model.loaded:
             raise RuntimeError("the model has no weights yet")
         self.model = model
@@ -116,7 +117,12 @@ class ModelRunner:
         self.max_tokens_per_step = max_tokens_per_step
         self.max_requests_per_step = max_requests_per_step
         self.workspace = Workspace(self.device)
-        self.max_blocks = -(-model.spec.max_positions // cache.page_size)
+        self.max_positions = min(model.spec.max_positions, max_positions or model.spec.max_positions)
+        self.max_blocks = -(-self.max_positions // cache.page_size)
+        if not any(g.need.bounded for g in cache.groups):
+            # a request never holds more pages than its group's pool has, however many positions the model allows
+            # (a group that gives pages back keeps their places in the table, so its table grows with the position)
+            self.max_blocks = min(self.max_blocks, max([g.pool.num_pages for g in cache.groups] or [1]))
         t, r, g = max_tokens_per_step, max_requests_per_step, len(cache.groups)
         # fixed offsets (in int32 words) of every region of the metadata buffer
         self._off = {}
@@ -181,9 +187,8 @@ class ModelRunner:
             if not cache.has_request(e.rid):
                 raise KeyError(f"request {e.rid!r} is not live in the cache")
             s = cache.kv_len[e.rid]
-            if s + n > self.model.spec.max_positions:
-                raise ValueError(f"request {e.rid!r} would reach {s + n} tokens; the model's limit is "
-                                 f"{self.model.spec.max_positions}")
+            if s + n > self.max_positions:
+                raise ValueError(f"request {e.rid!r} would reach {s + n} tokens; the limit is {self.max_positions}")
             if min(e.tokens) < 0 or max(e.tokens) >= vocab:
                 raise ValueError(f"request {e.rid!r}: token id outside [0, {vocab})")
             for w in e.want:
@@ -336,7 +341,7 @@ class ModelRunner:
         for gi, g in enumerate(cache.groups):
             sm = region(host, f"slot_mapping{gi}")
             bt = region(host, f"block_table{gi}").reshape(r, max_blocks)
-            windowed = g.need.window is not None
+            windowed = g.need.bounded
             for i, e in enumerate(entries):
                 table = cache.block_table(gi, e.rid)
                 if windowed:     # entries of a windowed group turn to -1 as the window moves: no cached row

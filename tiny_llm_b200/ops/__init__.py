@@ -97,7 +97,7 @@ def replay_tape(tape) -> None:
 def knobs():
     """The module's switches that decide which kernels a step launches; a tape or graph holds for one setting of them."""
     return (force_generic, split_k, cluster_mask, attention_tc, decode_wide_ctas, decode_cluster_merge, qkv_fused_rows,
-            linear_skinny, generic_attention_split, split_mixed_attention, _pdl)
+            linear_skinny, generic_attention_split, split_mixed_attention, min_gru_segment, _pdl)
 
 
 def _i32(t: Optional[torch.Tensor], name: str):
@@ -126,8 +126,9 @@ def trace_dump():
 # ----------------------------------------------------------------------------- elementwise
 
 
-def embedding(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t, :] = table[tokens[t], :] as float32 (the residual stream is 32-bit)."""
+def embedding(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
+    """out[t, :] = table[tokens[t], :] as float32 (the residual stream is 32-bit); accumulate=True adds the rows
+    into `out` instead."""
     _need_cuda(tokens, table, out)
     _i32(tokens, "tokens")
     t, h = out.shape
@@ -135,7 +136,8 @@ def embedding(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> N
             or tokens.numel() != t:
         raise KernelError("embedding: shapes or dtypes do not fit")
     lib = build.load_library("elementwise")
-    _call(lib, lib.tllm_embedding, _ptr(tokens), _ptr(table), _ptr(out), t, h, _code(table.dtype), _stream())
+    _call(lib, lib.tllm_embedding_add if accumulate else lib.tllm_embedding, _ptr(tokens), _ptr(table), _ptr(out), t, h,
+          _code(table.dtype), _stream())
 
 
 def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
@@ -152,6 +154,101 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tenso
     lib = build.load_library("elementwise")
     _call(lib, lib.tllm_rms_norm, _ptr(x), _ptr(weight), _ptr(out), _ptr(rows), n, h, ctypes.c_float(eps),
                                   _code(out.dtype), _stream())
+
+
+def dyt_norm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, alpha: torch.Tensor, out: torch.Tensor,
+             rows: Optional[torch.Tensor] = None) -> None:
+    """out[r, :] = tanh(alpha * x[rows[r], :]) * weight + bias (Dynamic Tanh: no statistics); x, weight, bias and
+    the one-element `alpha` are float32 on the device."""
+    _need_cuda(x, weight, bias, alpha, out, rows)
+    _i32(rows, "rows")
+    h = x.shape[1]
+    n = out.shape[0]
+    if x.dtype != torch.float32 or any(v.dtype != torch.float32 for v in (weight, bias, alpha)) or \
+            not x.is_contiguous() or not out.is_contiguous() or out.shape[1] != h or weight.numel() != h or \
+            bias.numel() != h or alpha.numel() != 1 or not weight.is_contiguous() or not bias.is_contiguous() or \
+            (rows is None and n != x.shape[0]) or (rows is not None and rows.numel() != n):
+        raise KernelError("dyt_norm: shapes or dtypes do not fit")
+    lib = build.load_library("elementwise")
+    _call(lib, lib.tllm_dyt_norm, _ptr(x), _ptr(weight), _ptr(bias), _ptr(alpha), _ptr(out), _ptr(rows), n, h,
+          _code(out.dtype), _stream())
+
+
+def rope_pairs_kv_write(qkv: torch.Tensor, positions: torch.Tensor, freq: Optional[torch.Tensor], rot_dims: int,
+                        num_q_rows: int, num_k_rows: int, num_v_rows: int, key_dim: int, value_dim: int,
+                        k_cache: torch.Tensor, v_cache: torch.Tensor, slot_mapping: torch.Tensor) -> None:
+    """Rows of `qkv`: num_q_rows query rows and num_k_rows key rows of key_dim values, then num_v_rows value rows of
+    value_dim values.  The first rot_dims values of every query and key row are rotated pairwise (value 2i with
+    2i + 1) by positions[t] * freq[i], in 32-bit; queries are rewritten in place, keys and values go to their pages
+    (k_cache [pages, num_k_rows, page_size, key_dim], v_cache [pages, num_v_rows, page_size, value_dim])."""
+    _need_cuda(qkv, positions, freq, k_cache, v_cache, slot_mapping)
+    _i32(positions, "positions")
+    _i32(slot_mapping, "slot_mapping")
+    t, width = qkv.shape
+    want = (num_q_rows + num_k_rows) * key_dim + num_v_rows * value_dim
+    if width != want or qkv.stride(1) != 1:
+        raise KernelError(f"rope_pairs_kv_write: rows of {width} values, expected {want}")
+    if k_cache.dtype != qkv.dtype or v_cache.dtype != qkv.dtype or \
+            k_cache.shape[1] != num_k_rows or k_cache.shape[3] != key_dim or k_cache.stride(3) != 1 or \
+            k_cache.stride(2) != key_dim or v_cache.shape[1] != num_v_rows or v_cache.shape[3] != value_dim or \
+            v_cache.stride(3) != 1 or v_cache.stride(2) != value_dim or k_cache.shape[2] != v_cache.shape[2]:
+        raise KernelError("rope_pairs_kv_write: cache layout does not fit")
+    if rot_dims and (freq is None or freq.dtype != torch.float32 or not freq.is_contiguous() or freq.numel() * 2 != rot_dims):
+        raise KernelError("rope_pairs_kv_write: the frequency table does not fit")
+    lib = build.load_library("elementwise")
+    _call(lib, lib.tllm_rope_pairs_kv_write, _ptr(qkv), _ptr(positions), _ptr(freq if rot_dims else None), rot_dims, t,
+          num_q_rows, num_k_rows, num_v_rows, key_dim, value_dim, qkv.stride(0), _ptr(k_cache), _ptr(v_cache),
+          _ptr(slot_mapping), k_cache.shape[2], ctypes.c_longlong(k_cache.stride(0)), ctypes.c_longlong(k_cache.stride(1)),
+          ctypes.c_longlong(v_cache.stride(0)), ctypes.c_longlong(v_cache.stride(1)), _code(qkv.dtype), _stream())
+
+
+def diff_combine(maps_out: torch.Tensor, lq1: torch.Tensor, lk1: torch.Tensor, lq2: torch.Tensor, lk2: torch.Tensor,
+                 diff: float, eps: float, out: torch.Tensor) -> None:
+    """maps_out: float32 [T, heads, 2, vd], the outputs a1, a2 of a head's two score maps.  With
+    lam = exp(sum(lq1 * lk1)) - exp(sum(lq2 * lk2)) + diff:  o = a1 - lam * a2;  out[T, heads * vd] =
+    o / sqrt(mean(o^2) + eps) * (1 - diff), all in 32-bit."""
+    _need_cuda(maps_out, lq1, lk1, lq2, lk2, out)
+    t, heads, two, vd = maps_out.shape
+    kd = lq1.numel()
+    if two != 2 or maps_out.dtype != torch.float32 or not maps_out.is_contiguous() or out.shape != (t, heads * vd) or \
+            not out.is_contiguous() or any(v.dtype != torch.float32 or v.numel() != kd or not v.is_contiguous()
+                                           for v in (lq1, lk1, lq2, lk2)):
+        raise KernelError("diff_combine: shapes or dtypes do not fit")
+    lib = build.load_library("elementwise")
+    _call(lib, lib.tllm_diff_combine, _ptr(maps_out), _ptr(lq1), _ptr(lk1), _ptr(lq2), _ptr(lk2), kd,
+          ctypes.c_float(diff), ctypes.c_float(eps), _ptr(out), ctypes.c_longlong(t * heads), vd, _code(out.dtype), _stream())
+
+
+# Portions of at least this many tokens run the minGRU recurrence in segments (two kernels, every segment a thread
+# per channel) instead of one thread per channel walking the whole portion; 0 turns the segments off.  The 32-bit
+# path always walks serially: its results do not depend on how a sequence was cut into steps, to the bit.
+min_gru_segment = int(os.environ.get("TLLM_MINGRU_SEGMENT", "64"))
+
+
+def min_gru_scan(zug: torch.Tensor, bias_z: torch.Tensor, bias_u: torch.Tensor, state: torch.Tensor,
+                 batch, out: torch.Tensor, workspace=None) -> None:
+    """The minGRU recurrence over the step's tokens.  zug [T, 3 * width]: the projections [z | u | g];
+    S_t = (1 - z_t) S_(t-1) + z_t c_t with z_t = sigmoid(z + bias_z), c_t = u + bias_u + 1/2 where that is >= 0 and
+    sigmoid(u + bias_u) below; out[t] = S_t * silu(g).  state [slots, width] float32 holds S per request
+    (batch.slots names each request's row) and is carried from step to step."""
+    _need_cuda(zug, bias_z, bias_u, state, out)
+    t, w3 = zug.shape
+    width = w3 // 3
+    if w3 != 3 * width or zug.stride(1) != 1 or out.shape != (t, width) or not out.is_contiguous() or \
+            out.dtype != zug.dtype or state.dtype != torch.float32 or not state.is_contiguous() or \
+            state.shape[1] != width or any(b.dtype != torch.float32 or b.numel() != width or not b.is_contiguous()
+                                           for b in (bias_z, bias_u)):
+        raise KernelError("min_gru_scan: shapes or dtypes do not fit")
+    seg, summary = 0, None
+    if zug.dtype == torch.bfloat16 and workspace is not None and min_gru_segment > 0 and \
+            batch.max_q_len >= 2 * min_gru_segment:
+        seg = min_gru_segment
+        segs = -(-batch.max_q_len // seg)
+        summary = workspace.get("min_gru_summary", (batch.num_requests * (2 * segs + 1) * width,), torch.float32)
+    lib = build.load_library("recurrence")
+    _call(lib, lib.tllm_min_gru_scan, _ptr(zug), zug.stride(0), _ptr(bias_z), _ptr(bias_u), _ptr(state),
+          _ptr(batch.slots), _ptr(batch.cu_q), _ptr(out), width, batch.num_requests, batch.max_q_len, seg,
+          _ptr(summary), _code(zug.dtype), _stream())
 
 
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, block: int, consume: bool = False) -> None:
@@ -581,6 +678,34 @@ def paged_attention(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_d
         -1 if generic_attention_split is None else int(generic_attention_split), _stream())
 
 
+def paged_attention_maps(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, maps: int, key_dim: int, value_dim: int,
+                         k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor, batch,
+                         out: torch.Tensor, scale: float, window: Optional[int] = None,
+                         chunk: Optional[int] = None) -> None:
+    """Attention with `maps` score maps per head over the same values, key rows of key_dim and value rows of
+    value_dim values: query rows [head][map][key_dim] at the front of each `qkv` row, k_cache
+    [pages, num_kv_heads * maps, page_size, key_dim], v_cache [pages, num_kv_heads, page_size, value_dim]; out
+    [T, num_heads * maps * value_dim] in the cache's dtype or float32.  `chunk`: a key is visible only inside the
+    query's chunk of that many positions (counted from position 0).  Runs on the CUDA cores in 32-bit."""
+    _need_cuda(qkv, k_cache, v_cache, block_table, out)
+    _i32(block_table, "block_table")
+    t = qkv.shape[0]
+    if out.shape != (t, num_heads * maps * value_dim) or not out.is_contiguous() or \
+            out.dtype not in (qkv.dtype, torch.float32) or k_cache.dtype != qkv.dtype or v_cache.dtype != qkv.dtype or \
+            k_cache.stride(3) != 1 or k_cache.stride(2) != key_dim or k_cache.shape[1] != num_kv_heads * maps or \
+            k_cache.shape[3] != key_dim or v_cache.stride(3) != 1 or v_cache.stride(2) != value_dim or \
+            v_cache.shape[1] != num_kv_heads or v_cache.shape[3] != value_dim or k_cache.shape[2] != v_cache.shape[2]:
+        raise KernelError("paged_attention_maps: shapes or dtypes do not fit")
+    lib = build.load_library("attention_generic")
+    _call(lib, lib.tllm_paged_attention_maps,
+          _ptr(qkv), qkv.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
+          _ptr(batch.token_request), _ptr(batch.positions), _ptr(out), t, num_heads, num_kv_heads, maps, key_dim,
+          value_dim, k_cache.shape[2], ctypes.c_longlong(k_cache.stride(0)), ctypes.c_longlong(k_cache.stride(1)),
+          ctypes.c_longlong(v_cache.stride(0)), ctypes.c_longlong(v_cache.stride(1)), ctypes.c_float(scale),
+          int(window or 0), int(chunk or 0), _code(qkv.dtype), 1 if out.dtype == torch.float32 else 0,
+          -1 if generic_attention_split is None else int(generic_attention_split), _stream())
+
+
 def attention_tc_timing(head_dim: int = 64) -> Optional[dict]:
     """Cycles that the roles of the prompt-attention kernel's first CTA spent per phase since the last call, or
     None if the kernel was not built with TLLM_NVCC_FLAGS_ATTENTION_TC=-DTLLM_ATT_TIMING=1."""
@@ -635,7 +760,7 @@ def sample(logits: torch.Tensor, work: torch.Tensor, temperature: torch.Tensor, 
                                 _ptr(seeds), _ptr(counters), _ptr(out), _ptr(status), _stream())
 
 
-ALL_LIBRARIES = ("elementwise", "linear_generic", "linear_tc", "attention_generic", "sampling")
+ALL_LIBRARIES = ("elementwise", "linear_generic", "linear_tc", "attention_generic", "recurrence", "sampling")
 
 
 ATTENTION_HEAD_DIMS = (16, 32, 48, 64, 128)   # head sizes `build_all` compiles ahead; others compile on first use

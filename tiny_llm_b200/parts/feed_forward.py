@@ -23,6 +23,13 @@ def interleave_gate_up(wg: torch.Tensor, wu: torch.Tensor, block: int) -> torch.
     return torch.stack([wg.view(g, block, h), wu.view(g, block, h)], dim=1).reshape(2 * i, h).contiguous()
 
 
+def scaled_matrix(w: torch.Tensor, scale: float) -> torch.Tensor:
+    """`w` times a constant of the model, multiplied in 32-bit and rounded once to the matrix's own type."""
+    if scale == 1.0:
+        return w
+    return (w.to(torch.float32) * scale).to(w.dtype).contiguous()
+
+
 def gate_up_block(intermediate_size: int) -> int:
     for b in (128, 64, 32, 16, 8, 4, 2):
         if intermediate_size % b == 0:
@@ -33,23 +40,28 @@ def gate_up_block(intermediate_size: int) -> int:
 class SwiGLU:
     graph_safe = True   # launches kernels only: a step through this part can be captured in a CUDA graph
 
-    def __init__(self, hidden_size: int, intermediate_size: int):
+    def __init__(self, hidden_size: int, intermediate_size: int,
+                 names=("gate_proj.weight", "up_proj.weight", "down_proj.weight"), out_scale: float = 1.0):
+        """`names`: what the gate, up and down matrices are called behind the part's prefix.  `out_scale`: a
+        constant the part's output is multiplied by; it is folded into the down matrix when that is loaded."""
         self.hidden_size = hidden_size
         self.intermediate_size = intermediate_size
+        self.names = tuple(names)
+        self.out_scale = float(out_scale)
         self.block = gate_up_block(intermediate_size)
         self.w_gate_up = None
         self.w_down = None
 
     def weight_specs(self, prefix: str):
         i, h = self.intermediate_size, self.hidden_size
-        return [WeightSpec(prefix + "gate_proj.weight", (i, h), COMPUTE),
-                WeightSpec(prefix + "up_proj.weight", (i, h), COMPUTE),
-                WeightSpec(prefix + "down_proj.weight", (h, i), COMPUTE)]
+        g, u, d = self.names
+        return [WeightSpec(prefix + g, (i, h), COMPUTE), WeightSpec(prefix + u, (i, h), COMPUTE),
+                WeightSpec(prefix + d, (h, i), COMPUTE)]
 
     def load(self, prefix: str, weights) -> None:
-        self.w_gate_up = interleave_gate_up(weights[prefix + "gate_proj.weight"],
-                                            weights[prefix + "up_proj.weight"], self.block)
-        self.w_down = weights[prefix + "down_proj.weight"]
+        g, u, d = self.names
+        self.w_gate_up = interleave_gate_up(weights[prefix + g], weights[prefix + u], self.block)
+        self.w_down = scaled_matrix(weights[prefix + d], self.out_scale)
 
     def forward(self, ctx, h, resid) -> None:
         t = h.shape[0]

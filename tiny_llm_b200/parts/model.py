@@ -16,20 +16,25 @@ from .registry import build_block, build_part, register_block
 
 
 class Block:
-    """The pre-norm residual block: x += mixer(norm1(x)); x += ffn(norm2(x))."""
+    """The pre-norm residual block: x += s * mixer(norm1(x)); x += s * ffn(norm2(x)), with s the layer's
+    `residual_scale` (the parts take it as `out_scale` and fold it into their output matrices).  A layer without
+    a feed-forward names neither `ffn` nor `norm2` and ends after the first line."""
 
     def __init__(self, spec: LayerSpec, shares_cache: bool = False):
-        for role in ("norm1", "mixer", "norm2", "ffn"):
+        for role in ("norm1", "mixer"):
             if getattr(spec, role) is None:
                 raise ValueError(f"layer {spec.prefix!r}: a pre_norm block needs a {role}")
+        if (spec.ffn is None) != (spec.norm2 is None):
+            raise ValueError(f"layer {spec.prefix!r}: a pre_norm block has a norm2 exactly when it has a feed-forward")
         self.spec = spec
+        scale = {} if spec.residual_scale == 1.0 else {"out_scale": spec.residual_scale}
         self.norm1 = build_part("norm", spec.norm1)
-        self.norm2 = build_part("norm", spec.norm2)
-        self.mixer = build_part("mixer", spec.mixer, **({"shares_cache": True} if shares_cache else {}))
-        self.ffn = build_part("ffn", spec.ffn)
+        self.mixer = build_part("mixer", spec.mixer, **scale, **({"shares_cache": True} if shares_cache else {}))
+        self.norm2 = None if spec.ffn is None else build_part("norm", spec.norm2)
+        self.ffn = None if spec.ffn is None else build_part("ffn", spec.ffn, **scale)
 
     def parts(self):
-        return [self.norm1, self.mixer, self.norm2, self.ffn]
+        return [p for p in (self.norm1, self.mixer, self.norm2, self.ffn) if p is not None]
 
     def _prefixes(self):
         p = self.spec.prefix
@@ -37,21 +42,25 @@ class Block:
 
     def weight_specs(self) -> List[WeightSpec]:
         n1, mx, n2, ff = self._prefixes()
-        return (self.norm1.weight_specs(n1) + self.mixer.weight_specs(mx) +
-                self.norm2.weight_specs(n2) + self.ffn.weight_specs(ff))
+        specs = self.norm1.weight_specs(n1) + self.mixer.weight_specs(mx)
+        if self.ffn is not None:
+            specs += self.norm2.weight_specs(n2) + self.ffn.weight_specs(ff)
+        return specs
 
     def load(self, weights) -> None:
         n1, mx, n2, ff = self._prefixes()
         self.norm1.load(n1, weights)
         self.mixer.load(mx, weights)
-        self.norm2.load(n2, weights)
-        self.ffn.load(ff, weights)
+        if self.ffn is not None:
+            self.norm2.load(n2, weights)
+            self.ffn.load(ff, weights)
 
     def forward(self, ctx, resid, cache) -> None:
         h = self.norm1.forward(ctx, resid)
         self.mixer.forward(ctx, h, resid, cache)
-        h = self.norm2.forward(ctx, resid)
-        self.ffn.forward(ctx, h, resid)
+        if self.ffn is not None:
+            h = self.norm2.forward(ctx, resid)
+            self.ffn.forward(ctx, h, resid)
 
 
 register_block("pre_norm", Block)
@@ -66,6 +75,9 @@ class DecoderModel:
             if call.reads_cache_of is not None and not 0 <= call.reads_cache_of < pos:
                 raise ValueError(f"run order entry {pos} reads the cache of entry {call.reads_cache_of}, "
                                  f"which does not run before it")
+        if spec.after_embedding is not None and any(c.add_embedding for c in spec.order):
+            raise ValueError("a run order that adds the embedding output again cannot be combined with a hook that "
+                             "rewrites the stream after the embedding")
         shared = {c.layer for c in spec.order if c.reads_cache_of is not None}
         owning = {c.layer for c in spec.order if c.reads_cache_of is None}
         if shared & owning:
@@ -77,6 +89,9 @@ class DecoderModel:
         self.embed = None
         self.lm_head = None
         self.loaded = False
+        # a callable(position in the run order, float32 stream [T, H]) called after every layer call: for tests and
+        # debugging only (a runner built around a model with a probe must not capture or tape its steps)
+        self.probe = None
         # a part that synchronises or computes on the host must not be captured; parts say so themselves
         parts = [self.final_norm] + [x for b in self.blocks for x in b.parts()] + \
             [h for h in (self.after_embedding, self.on_logits) if h is not None]
@@ -134,7 +149,11 @@ class DecoderModel:
             self.after_embedding.forward(ctx, resid)
         for pos, call in enumerate(s.order):
             owner = pos if call.reads_cache_of is None else call.reads_cache_of
+            if call.add_embedding:   # the embedding output is the table's rows again: gathered and added in one kernel
+                ops.embedding(b.tokens, self.embed, resid, accumulate=True)
             self.blocks[call.layer].forward(ctx, resid, ctx.cache_view(owner))
+            if self.probe is not None:
+                self.probe(pos, resid)
         if b.num_logits == 0:
             return None
         h = self.final_norm.forward(ctx, resid, rows=b.logit_rows)

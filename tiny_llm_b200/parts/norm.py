@@ -1,4 +1,4 @@
-"""RMSNorm: y_j = (w_j x_j) / sqrt(mean_j(x_j^2) + eps), statistics in 32-bit
+"""Norms.  RMSNorm: y_j = (w_j x_j) / sqrt(mean_j(x_j^2) + eps), statistics in 32-bit
 (tiny_llm/ops/cuda/norm.cu:16-49).  Any width; the reference stops at 2048."""
 from __future__ import annotations
 
@@ -28,4 +28,32 @@ class RMSNorm:
         return out
 
 
+class DynamicTanh:
+    """Dynamic Tanh: y_j = tanh(alpha x_j) w_j + b_j with one learned number alpha.  It takes the place of a norm and
+    computes no mean or variance, so a row's output does not depend on the row's other values.  The weight is
+    stored under the part's own name, the bias and alpha beside it as `<name>.b` and `<name>.alpha`."""
+    graph_safe = True
+
+    def __init__(self, size: int):
+        self.size = size
+        self.weight = self.bias = self.alpha = None
+
+    def weight_specs(self, prefix: str):
+        return [WeightSpec(prefix, (self.size,), FLOAT32),
+                WeightSpec(prefix + ".b", (self.size,), FLOAT32, init=("normal", 0.05)),
+                WeightSpec(prefix + ".alpha", (), FLOAT32, init=("const", 0.75))]
+
+    def load(self, prefix: str, weights) -> None:
+        self.weight = weights[prefix]
+        self.bias = weights[prefix + ".b"]
+        self.alpha = weights[prefix + ".alpha"].reshape(1).contiguous()
+
+    def forward(self, ctx, x, rows=None):
+        n = x.shape[0] if rows is None else rows.shape[0]
+        out = ctx.workspace.get("norm_out", (n, self.size), ctx.dtype)
+        ops.dyt_norm(x, self.weight, self.bias, self.alpha, out, rows)
+        return out
+
+
 register_part("norm", "rms_norm", RMSNorm)
+register_part("norm", "dynamic_tanh", DynamicTanh)

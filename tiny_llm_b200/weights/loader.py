@@ -31,6 +31,9 @@ class WeightSpec:
     shape: Tuple[int, ...]
     keep: str = COMPUTE
     alias_of: Optional[str] = None
+    # how random-weights mode fills the tensor when the default (matrices N(0, initializer_range), float32 vectors 1)
+    # does not suit it: ("normal", std), ("const", value) or ("uniform", low, high)
+    init: Optional[Tuple] = None
 
 
 def _convert(t: torch.Tensor, spec: WeightSpec, dtype: torch.dtype) -> torch.Tensor:

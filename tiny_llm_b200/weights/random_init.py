@@ -33,7 +33,13 @@ def random_state(specs: Mapping[str, WeightSpec], seed: int, std: float, dtype: 
     for name, s in specs.items():
         if s.keep == INT32:
             out[name] = torch.zeros(s.shape, dtype=torch.int32, device=device)
-        elif s.keep == FLOAT32 and len(s.shape) == 1:
+        elif s.init is not None and s.init[0] == "const":
+            out[name] = torch.full(s.shape, float(s.init[1]), dtype=dtype, device=device)
+        elif s.init is not None and s.init[0] == "uniform":
+            t = torch.empty(s.shape, dtype=torch.float32)
+            t.uniform_(float(s.init[1]), float(s.init[2]), generator=_generator(seed, name))
+            out[name] = t.to(dtype).to(device)
+        elif s.init is None and s.keep == FLOAT32 and len(s.shape) == 1:
             out[name] = torch.ones(s.shape, dtype=dtype, device=device)
         else:
             g = _generator(seed, name)
@@ -42,7 +48,7 @@ def random_state(specs: Mapping[str, WeightSpec], seed: int, std: float, dtype: 
                 dg.manual_seed(g.initial_seed())
                 g = dg
             t = torch.empty(s.shape, dtype=torch.float32, device=device)
-            t.normal_(0.0, std, generator=g)
+            t.normal_(0.0, float(s.init[1]) if s.init is not None else std, generator=g)
             out[name] = t.to(dtype)
     return out
 
