@@ -391,6 +391,192 @@ def reference_arm(steps, warmup):
     return 0
 
 
+# ----------------------------------------------------------------------------- another design beside the flagship
+# `--design dunelix`: prefill and decode of a Dunelix model (minGRU and chunked differential-attention layers, Dynamic
+# Tanh) at layer sizes of the TinyLlama shape, beside the Llama decoder at equal width, feed-forward size, layers and
+# vocabulary, and the new kernels alone beside their like kernels of the Llama path, each against its roofline.
+DESIGN_LAYERS = 8
+
+
+def dunelix_shape(layers=DESIGN_LAYERS, width=2048, ff=5632, vocab=32000, chunk=1024):
+    att = {"type": "attention", "mixer": {"heads": 16, "kv_heads": 4, "dim": 64, "vdim": 128, "scale": 0.125, "diff": 0.4,
+                                          "mask": {"size": chunk}, "rot": {"dims": 64, "base": 10000.0}},
+           "mlp": {"kind": "dense", "ff": ff}}
+    gru = {"type": "mingru", "mixer": {"width": width}, "mlp": {"kind": "dense", "ff": ff}}
+    return {"architecture": "Dunelix", "vocab": vocab, "width": width, "residual_mult": 0.5, "norm": {"eps": 1e-6},
+            "initializer_range": 0.02, "layers": [att if i % 4 == 3 else gru for i in range(layers)]}
+
+
+def build_design(shape, dtype, device, seed=7):
+    from tiny_llm_b200.config import config_from_dict
+    from tiny_llm_b200.parts import DecoderModel
+    from tiny_llm_b200.weights import load_state, random_state
+    cfg = config_from_dict(shape)
+    model = DecoderModel(cfg.model_spec())
+    specs = model.weight_specs()
+    model.load(load_state(specs, random_state(specs, seed, cfg.initializer_range, dtype, device=device), dtype, device))
+    return cfg, model
+
+
+def spec_weight_bytes(model, itemsize):
+    """Bytes of every weight a decode step reads once (all but the embedding table, whose rows are gathered)."""
+    from tiny_llm_b200.weights import COMPUTE
+    total = 0
+    for name, w in model.weight_specs().items():
+        if name == model.spec.embed_name:
+            continue
+        n = 1
+        for d in w.shape:
+            n *= d
+        total += n * (itemsize if w.keep == COMPUTE else 4)
+    return total
+
+
+def design_decode_bytes(model, runner, batch, mean_ctx, itemsize):
+    """Weights once, the keys and values each request can see (a chunked group: the part of its chunk behind it),
+    and the recurrent states read and written."""
+    total = spec_weight_bytes(model, itemsize)
+    for g in runner.cache.groups:
+        seen = mean_ctx if g.need.chunk is None else (mean_ctx % g.need.chunk or g.need.chunk)
+        total += batch * seen * g.bytes_per_token(itemsize)
+    total += 2 * batch * sum(4 * n.shape[0] for n in runner.cache.slots.needs)
+    return total
+
+
+def time_kernel(fn, flush, repeats=20):
+    """Median microseconds of fn() with L2 flushed (a write of a buffer larger than L2) before every timed call."""
+    import torch
+    for _ in range(3):
+        fn()
+    times = []
+    for _ in range(repeats):
+        flush.zero_()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        fn()
+        t1.record()
+        torch.cuda.synchronize()
+        times.append(t0.elapsed_time(t1) * 1e3)
+    return statistics.median(times)
+
+
+def design_kernels(dtype, device, pk, tokens=2048):
+    """The new kernels alone at the sizes of one layer of the --design shape and `tokens` tokens of one prompt, and
+    their like kernels of the Llama path at equal sizes: microseconds, achieved GB/s or TFLOP/s, share of the peak."""
+    import types
+    import torch
+    from tiny_llm_b200 import ops
+    from tiny_llm_b200.engine import Workspace
+    t, width, heads, kvh, kd, vd, chunk, page = tokens, 2048, 16, 4, 64, 128, 1024, PAGE
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=device)
+    out = {}
+
+    def mem(name, us, nbytes):
+        out[name] = {"us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1), "frac": round(nbytes / us / 1e3 / pk["hbm_gbs"], 3)}
+
+    def flop(name, us, flops):
+        out[name] = {"us": round(us, 2), "tflops": round(flops / us / 1e6, 1), "frac": round(flops / us / 1e6 / pk["bf16_tflops"], 3)}
+
+    x = torch.randn(t, width, device=device)
+    w, b, alpha = torch.ones(width, device=device), torch.zeros(width, device=device), torch.full((1,), 0.5, device=device)
+    y = torch.empty(t, width, dtype=dtype, device=device)
+    mem("dynamic_tanh", time_kernel(lambda: ops.dyt_norm(x, w, b, alpha, y), flush), t * width * 6)
+    mem("rms_norm (like)", time_kernel(lambda: ops.rms_norm(x, w, 1e-5, y), flush), t * width * 6)
+
+    zug = torch.randn(t, 3 * width, device=device).to(dtype)
+    bias = torch.zeros(width, device=device)
+    state = torch.zeros(4, width, device=device)
+    batch = types.SimpleNamespace(cu_q=i32([0, t]), slots=i32([1]), num_requests=1, max_q_len=t)
+    ws = Workspace(torch.device(device))
+    yy = torch.empty(t, width, dtype=dtype, device=device)
+    # segments read z and u twice: the algorithmic bytes are one read of [z|u|g] and one write of y
+    mem("min_gru_scan", time_kernel(lambda: ops.min_gru_scan(zug, bias, bias, state, batch, yy, ws), flush), t * width * 8)
+    gu = torch.randn(t, 2 * width, device=device).to(dtype)
+    mem("silu_mul (like)", time_kernel(lambda: ops.silu_mul(gu, yy, 128), flush), t * width * 6)
+
+    # one request of `t` tokens from position 0 in pages of its own
+    pages = -(-t // page)
+    table = i32([list(range(pages))])
+    slots = i32(list(range(t)))
+    pos = i32(list(range(t)))
+    meta = types.SimpleNamespace(token_request=i32([0] * t), positions=pos, cu_q=i32([0, t]), q_start=i32([0]),
+                                 num_requests=1, max_q_len=t, max_kv_len=t, num_leading_decodes=0)
+    maps = 2
+    qkv = torch.randn(t, (heads + kvh) * maps * kd + kvh * vd, device=device).to(dtype)
+    kc = torch.zeros(pages, kvh * maps, page, kd, dtype=dtype, device=device)
+    vc = torch.zeros(pages, kvh, page, vd, dtype=dtype, device=device)
+    freq = torch.pow(torch.tensor(10000.0), -torch.arange(kd // 2, dtype=torch.float32) * 2 / kd).to(device)
+    mem("rope_pairs_kv_write", time_kernel(lambda: ops.rope_pairs_kv_write(qkv, pos, freq, kd, heads * maps, kvh * maps, kvh, kd, vd,
+                                                                          kc, vc, slots), flush),
+        t * 2 * ((heads * maps * kd) * 2 + (kvh * maps * kd + kvh * vd) * 2))
+    per_map = torch.empty(t, heads * maps * vd, dtype=torch.float32, device=device)
+    # visible (query, key) pairs of a causal chunked mask
+    pairs = sum(min(p % chunk, p) + 1 for p in range(t))
+    att_flops = 2.0 * pairs * heads * maps * (kd + vd)
+    flop("attention, two maps, chunk 1024", time_kernel(lambda: ops.paged_attention_maps(
+        qkv, heads, kvh, maps, kd, vd, kc, vc, table, meta, per_map, 0.125, None, chunk), flush), att_flops)
+    comb = torch.empty(t, heads * vd, dtype=dtype, device=device)
+    lam = [torch.zeros(kd, device=device) for _ in range(4)]
+    mem("diff_combine", time_kernel(lambda: ops.diff_combine(per_map.view(t, heads, maps, vd), *lam, 0.4, 1e-6, comb), flush),
+        t * heads * vd * (8 + 2))
+    # the like kernels of the Llama path at equal width: 32 heads of 64, 4 key/value heads
+    lq = torch.randn(t, (32 + 8) * 64, device=device).to(dtype)
+    lkv = torch.zeros(2, pages, 4, page, 64, dtype=dtype, device=device)
+    cos = torch.ones(t, 32, device=device)
+    sin = torch.zeros(t, 32, device=device)
+    mem("rope_kv_write (like)", time_kernel(lambda: ops.rope_kv_write(lq, pos, cos, sin, 64, 32, 4, 64, lkv[0], lkv[1], slots), flush),
+        t * 2 * (32 * 64 * 2 + 8 * 64 * 2))
+    lo = torch.empty(t, 32 * 64, dtype=dtype, device=device)
+    causal = sum(p + 1 for p in range(t))
+    flop("attention (like: causal, 32 heads of 64)", time_kernel(lambda: ops.paged_attention(
+        lq, 32, 4, 64, lkv[0], lkv[1], table, meta, lo, 0.125, None, ws), flush), 2.0 * causal * 32 * (64 + 64))
+    return out
+
+
+def design_run(args, dtype, device, pk):
+    import gc
+    import torch
+    from tiny_llm_b200 import ops
+    from tiny_llm_b200.engine import make_runner
+    itemsize = 2 if dtype == torch.bfloat16 else 4
+    steps, warmup = min(max(1, args.steps), 32), max(3, min(args.warmup, 8))
+    out = torch.zeros(64, dtype=torch.int32, device=device)
+    result = {"design": "dunelix", "dtype": args.dtype, "layers": DESIGN_LAYERS, "peaks": pk["source"],
+              "sizes": "width 2048, feed-forward 5632, vocabulary 32000; minGRU width 2048; attention 16 heads x 2 maps of 64, "
+                       "4 key/value heads, values of 128, chunk 1024; every fourth layer attention; beside: Llama decoder, "
+                       "32 heads of 64, 4 key/value heads, equal width, feed-forward, layers and vocabulary",
+              "l2": "whole steps: weights larger than L2; kernels alone: L2 flushed before every timed call"}
+    sampler = ClockSampler().start()
+    for label in ("dunelix", "llama"):
+        if label == "dunelix":
+            cfg, model = build_design(dunelix_shape(), dtype, device)
+        else:
+            cfg, model = build_model(DESIGN_LAYERS, dtype, device)
+        runner = make_runner(model, dtype, device, max_tokens=64 * CONTEXT, page_size=PAGE, max_requests=64,
+                             max_tokens_per_step=2048, max_positions=CONTEXT)
+        rec = {}
+        for tt in (512, 2048):
+            ms = timed_prefill(runner, tt, repeats=3)
+            rec[f"prefill_{tt}"] = {"ms": round(ms, 3), "tokens_per_s": round(tt * 1e3 / ms, 1)}
+        for bsz in (8, 64):
+            ms, launched, ctx = timed_decode(runner, bsz, CONTEXT - (REPEATS * steps + warmup), steps, warmup, out, repeats=REPEATS)
+            moved = design_decode_bytes(model, runner, bsz, ctx, itemsize) if label == "dunelix" else \
+                decode_bytes(model, runner, bsz, ctx, itemsize)
+            rec[f"decode_b{bsz}"] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(bsz * 1e3 / ms, 1),
+                                     "hbm_frac": round(moved / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4), "gpu_launches": launched}
+        result[label] = rec
+        del runner, model
+        gc.collect()
+        torch.cuda.empty_cache()
+    result["clocks"] = sampler.stop()
+    if dtype == torch.bfloat16:
+        result["kernels"] = design_kernels(dtype, device, pk)
+    ops.check_status()
+    print(json.dumps(result))
+    return 0
+
+
 def main():
     global PAGE
     ap = argparse.ArgumentParser()
@@ -410,6 +596,9 @@ def main():
     ap.add_argument("--page-size", type=int, default=PAGE, help="tokens per page of the cache")
     ap.add_argument("--shape", default="tinyllama", choices=["tinyllama"] + list(OTHER_SHAPES),
                     help="layer sizes for --only runs (profiler captures of the other models' kernels)")
+    ap.add_argument("--design", default=None, choices=["dunelix"],
+                    help="instead of the flagship run: this design's prefill and decode at real layer sizes beside the Llama "
+                         "decoder at equal sizes, and its kernels beside their like kernels (one plain line, no record)")
     ap.add_argument("--quick", action="store_true",
                     help="leave out the workload points and the Llama-2-7B / Llama-3-8B layer sizes")
     args = ap.parse_args()
@@ -428,6 +617,8 @@ def main():
     device = "cuda:0"
     torch.cuda.set_device(0)
     pk = peaks()
+    if args.design:
+        return design_run(args, dtype, device, pk)
     if args.shape != "tinyllama" and args.only == "all":
         print("--shape goes with --only decode|prefill (the full run measures every shape)")
         return 2

@@ -97,7 +97,7 @@ def replay_tape(tape) -> None:
 def knobs():
     """The module's switches that decide which kernels a step launches; a tape or graph holds for one setting of them."""
     return (force_generic, split_k, cluster_mask, attention_tc, decode_wide_ctas, decode_cluster_merge, qkv_fused_rows,
-            linear_skinny, generic_attention_split, split_mixed_attention, min_gru_segment, _pdl)
+            linear_skinny, generic_attention_split, split_mixed_attention, min_gru_segment, attention_maps_tc, _pdl)
 
 
 def _i32(t: Optional[torch.Tensor], name: str):
@@ -678,6 +678,10 @@ def paged_attention(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_d
         -1 if generic_attention_split is None else int(generic_attention_split), _stream())
 
 
+# bfloat16 attention with several score maps per head on the tensor cores (False: the CUDA-core kernel; for measurements)
+attention_maps_tc = os.environ.get("TLLM_ATTENTION_MAPS_TC", "1") != "0"
+
+
 def paged_attention_maps(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, maps: int, key_dim: int, value_dim: int,
                          k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor, batch,
                          out: torch.Tensor, scale: float, window: Optional[int] = None,
@@ -686,7 +690,10 @@ def paged_attention_maps(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, m
     value_dim values: query rows [head][map][key_dim] at the front of each `qkv` row, k_cache
     [pages, num_kv_heads * maps, page_size, key_dim], v_cache [pages, num_kv_heads, page_size, value_dim]; out
     [T, num_heads * maps * value_dim] in the cache's dtype or float32.  `chunk`: a key is visible only inside the
-    query's chunk of that many positions (counted from position 0).  Runs on the CUDA cores in 32-bit."""
+    query's chunk of that many positions (counted from position 0).  `batch`: token_request and positions per token
+    (the CUDA-core kernel); cu_q, q_start per request, num_requests, max_q_len (the tensor-core kernel).
+    bfloat16 with a float32 output and sizes that are multiples of 16 runs on the tensor cores, everything else on
+    the CUDA cores in 32-bit."""
     _need_cuda(qkv, k_cache, v_cache, block_table, out)
     _i32(block_table, "block_table")
     t = qkv.shape[0]
@@ -696,6 +703,18 @@ def paged_attention_maps(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, m
             k_cache.shape[3] != key_dim or v_cache.stride(3) != 1 or v_cache.stride(2) != value_dim or \
             v_cache.shape[1] != num_kv_heads or v_cache.shape[3] != value_dim or k_cache.shape[2] != v_cache.shape[2]:
         raise KernelError("paged_attention_maps: shapes or dtypes do not fit")
+    if qkv.dtype == torch.bfloat16 and out.dtype == torch.float32 and not force_generic and attention_maps_tc and \
+            key_dim % 16 == 0 and value_dim % 16 == 0 and 16 <= key_dim <= 256 and 16 <= value_dim <= 256 and \
+            qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0:
+        # bfloat16: the tensor-core kernel compiled for this pair of sizes (prompt portions and decoded tokens alike)
+        lib = build.load_library("attention_maps_mma", flags=(f"-DTLLM_HEAD_DIM={key_dim}", f"-DTLLM_VALUE_DIM={value_dim}"))
+        _call(lib, lib.tllm_attention_maps_mma,
+              _ptr(qkv), qkv.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
+              _ptr(batch.cu_q), _ptr(batch.q_start), _ptr(out), t, batch.num_requests, batch.max_q_len, num_heads,
+              num_kv_heads, maps, key_dim, value_dim, k_cache.shape[2], ctypes.c_longlong(k_cache.stride(0)),
+              ctypes.c_longlong(k_cache.stride(1)), ctypes.c_longlong(v_cache.stride(0)),
+              ctypes.c_longlong(v_cache.stride(1)), ctypes.c_float(scale), int(window or 0), int(chunk or 0), _stream())
+        return
     lib = build.load_library("attention_generic")
     _call(lib, lib.tllm_paged_attention_maps,
           _ptr(qkv), qkv.stride(0), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1],
@@ -765,6 +784,7 @@ ALL_LIBRARIES = ("elementwise", "linear_generic", "linear_tc", "attention_generi
 
 ATTENTION_HEAD_DIMS = (16, 32, 48, 64, 128)   # head sizes `build_all` compiles ahead; others compile on first use
 ATTENTION_TC_HEAD_DIMS = (64, 128)            # head sizes the tcgen05 prompt-attention kernel is written for
+ATTENTION_MAPS_DIMS = ((64, 128),)            # (key size, value size) pairs of the multi-map kernel compiled ahead
 
 
 def build_all(verbose: bool = True):
@@ -774,4 +794,6 @@ def build_all(verbose: bool = True):
               for hd in ATTENTION_HEAD_DIMS]
     paths += [build.compile_library("attention_tc", flags=(f"-DTLLM_HEAD_DIM={hd}",), verbose=verbose)
               for hd in ATTENTION_TC_HEAD_DIMS]
+    paths += [build.compile_library("attention_maps_mma", flags=(f"-DTLLM_HEAD_DIM={kd}", f"-DTLLM_VALUE_DIM={vd}"), verbose=verbose)
+              for kd, vd in ATTENTION_MAPS_DIMS]
     return paths

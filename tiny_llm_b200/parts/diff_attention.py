@@ -75,7 +75,7 @@ class DiffAttention:
 
     def weight_specs(self, prefix: str):
         h, kd = self.hidden_size, self.key_dim
-        small = ("normal", 0.3)
+        small = ("normal", 0.1)
         return [WeightSpec(prefix + "q", (self.q_dim, h), COMPUTE), WeightSpec(prefix + "k", (self.k_dim, h), COMPUTE),
                 WeightSpec(prefix + "v", (self.v_dim, h), COMPUTE),
                 WeightSpec(prefix + "lq1", (kd,), FLOAT32, init=small), WeightSpec(prefix + "lk1", (kd,), FLOAT32, init=small),
