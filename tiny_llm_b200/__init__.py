@@ -1,8 +1,10 @@
-"""tiny_llm_b200: a small, whole inference engine for the Llama dense decoder on one B200 (sm_100a).
+"""tiny_llm_b200: a small, whole inference engine on one B200 (sm_100a) for decoders put together from parts: the
+Llama dense decoder, and Dunelix (minGRU and chunked differential-attention layers under Dynamic Tanh, with a span
+of layers that may run several times).
 
 config/    typed configuration and the architecture registry
 weights/   safetensors by tensor name, random-weights mode
-parts/     norm, position encoding, mixer, feed-forward, block, model: put together from specs
+parts/     norm, position encoding, mixer (attention or recurrent), feed-forward, block, model: put together from specs
 cache/     paged keys and values with block tables per request, layer groups, state slots
 engine/    the step function, the scheduler and the generate loop
 sampling/  greedy, temperature, top-k, top-p

@@ -1,5 +1,5 @@
-// Attention of the step's queries over the paged cache on the CUDA cores, any key size that is a
-// multiple of 8 and any value size up to 256 (the two may differ), any number of heads and groups, any
+// Attention of the step's queries over the paged cache on the CUDA cores, any key size and any value
+// size up to 256 (the two may differ; key rows whose bytes are a multiple of 16 are read with 16-byte loads), any number of heads and groups, any
 // page size.  It is the attention of the true 32-bit path and the fallback of the bfloat16 path.
 //
 // Heads.  A query head has `maps` score maps, each an attention of its own over the same values: the
@@ -38,6 +38,7 @@ constexpr int MAX_HD = 256;
 // Where the rows of the cache lie and which keys are visible; `nq` and `nk` count (head, map) rows.
 struct Geometry {
   int nq, nk, maps, kd, vd, page_size, window, chunk;
+  int kvec;   // key rows are read with 16-byte loads (their size and strides allow it); else value by value, same order
   long long k_page_stride, k_head_stride, v_page_stride, v_head_stride;
 };
 __device__ __forceinline__ int lowest_key(const Geometry& g, int p) {
@@ -88,12 +89,16 @@ __device__ __forceinline__ void attend_tile(Softmax<OD>& st, int j0, int lo, int
     row_off = (long long)page * g.v_page_stride + (long long)vh * g.v_head_stride + (long long)(j % page_size) * vd;
     const T* krow = kcache + (long long)page * g.k_page_stride + (long long)kh * g.k_head_stride + (long long)(j % page_size) * hd;
     float acc = 0.f;
+    if (g.kvec) {
 #pragma unroll 4
-    for (int d = 0; d < hd; d += Vec<T>::N) {
-      float kv[Vec<T>::N];
-      load16(krow + d, kv);
+      for (int d = 0; d < hd; d += Vec<T>::N) {
+        float kv[Vec<T>::N];
+        load16(krow + d, kv);
 #pragma unroll
-      for (int e = 0; e < Vec<T>::N; ++e) acc = fmaf(q_row[d + e], kv[e], acc);
+        for (int e = 0; e < Vec<T>::N; ++e) acc = fmaf(q_row[d + e], kv[e], acc);
+      }
+    } else {
+      for (int d = 0; d < hd; ++d) acc = fmaf(q_row[d], to_f32(krow[d]), acc);
     }
     s = acc;
   }
@@ -163,14 +168,22 @@ __device__ __forceinline__ void attend_tile_grouped(Softmax<OD> (&st)[GH], int n
     float acc[GH];
 #pragma unroll
     for (int i = 0; i < GH; ++i) acc[i] = 0.f;
+    if (g.kvec) {
 #pragma unroll 2
-    for (int d = 0; d < hd; d += Vec<T>::N) {
-      float kv[Vec<T>::N];
-      load16(krow + d, kv);
+      for (int d = 0; d < hd; d += Vec<T>::N) {
+        float kv[Vec<T>::N];
+        load16(krow + d, kv);
 #pragma unroll
-      for (int i = 0; i < GH; ++i)
+        for (int i = 0; i < GH; ++i)
 #pragma unroll
-        for (int e = 0; e < Vec<T>::N; ++e) acc[i] = fmaf(q_rows[i][d + e], kv[e], acc[i]);
+          for (int e = 0; e < Vec<T>::N; ++e) acc[i] = fmaf(q_rows[i][d + e], kv[e], acc[i]);
+      }
+    } else {
+      for (int d = 0; d < hd; ++d) {
+        const float kvd = to_f32(krow[d]);
+#pragma unroll
+        for (int i = 0; i < GH; ++i) acc[i] = fmaf(q_rows[i][d], kvd, acc[i]);
+      }
     }
 #pragma unroll
     for (int i = 0; i < GH; ++i) s[i] = acc[i];
@@ -410,14 +423,13 @@ extern "C" int tllm_paged_attention_maps(const void* q, int q_row_stride, const 
                                          int chunk, int dtype, int out_f32, int split_override, void* stream) {
   TLLM_REQUIRE(n_tokens > 0 && nq > 0 && nkv > 0 && nq % nkv == 0 && maps > 0,
                "attention: %d tokens, %d heads, %d key/value heads (heads must be a multiple of key/value heads)", n_tokens, nq, nkv);
-  TLLM_REQUIRE(kd >= 8 && kd <= MAX_HD && kd % 8 == 0 && vd >= 1 && vd <= MAX_HD,
-               "attention: key size %d / value size %d is not built (keys: multiples of 8 up to %d, values: up to %d)", kd, vd, MAX_HD, MAX_HD);
+  TLLM_REQUIRE(kd >= 1 && kd <= MAX_HD && vd >= 1 && vd <= MAX_HD,
+               "attention: key size %d / value size %d is not built (both up to %d)", kd, vd, MAX_HD);
   TLLM_REQUIRE(page_size > 0 && max_blocks > 0 && window >= 0 && chunk >= 0, "attention: page size %d, %d blocks, window %d, chunk %d", page_size, max_blocks, window, chunk);
   const int elem = dtype == TLLM_F32 ? 4 : 2;
   TLLM_REQUIRE(dtype == TLLM_F32 || dtype == TLLM_BF16, "attention: unknown dtype code %d", dtype);
-  TLLM_REQUIRE(((size_t)kcache % 16) == 0 && (k_page_stride * elem) % 16 == 0 && (k_head_stride * elem) % 16 == 0,
-               "attention: key rows must be 16-byte aligned");
   Geometry g;
+  g.kvec = (kd * elem) % 16 == 0 && ((size_t)kcache % 16) == 0 && (k_page_stride * elem) % 16 == 0 && (k_head_stride * elem) % 16 == 0;
   g.nq = nq * maps; g.nk = nkv * maps; g.maps = maps; g.kd = kd; g.vd = vd; g.page_size = page_size; g.window = window;
   g.chunk = chunk; g.k_page_stride = k_page_stride; g.k_head_stride = k_head_stride; g.v_page_stride = v_page_stride;
   g.v_head_stride = v_head_stride;

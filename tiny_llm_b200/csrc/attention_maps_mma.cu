@@ -51,25 +51,43 @@ __device__ __forceinline__ int lowest_key(const MapsParams& p, int pos) {
   return max(lo, 0);
 }
 
-// One tile: 64 key rows of KD values and 64 value rows of VD values, every 16-byte piece a copy of its own; rows
-// outside [j_begin, j_end] or without a page are zero-filled (a value row that was never written must not reach
-// the product: 0 x NaN).
+// One tile: 64 key rows of KD values and 64 value rows of VD values.  Thread t looks up the page of one row (0..63
+// keys, 64..127 values); the copies are then issued so that consecutive lanes fetch consecutive 16-byte pieces of a
+// row, the row's address coming from its lane by shuffle.  Rows outside [j_begin, j_end] or without a page are
+// zero-filled (a value row that was never written must not reach the product: 0 x NaN).
 __device__ __forceinline__ void load_tile(__nv_bfloat16* k_dst, __nv_bfloat16* v_dst, const PageLookup& pages, int j0,
                                           int j_begin, int j_end, int kh, int vh, const MapsParams& p, int tid) {
-  constexpr int KC = KD / 8, VC = VD / 8;
-  for (int idx = tid; idx < BN * (KC + VC); idx += 128) {
-    const bool is_v = idx >= BN * KC;
-    const int local = is_v ? idx - BN * KC : idx;
-    const int r = is_v ? local / VC : local / KC, c = is_v ? local % VC : local % KC;
-    const int j = j0 + r;
-    bool ok = j >= j_begin && j <= j_end;
-    const int page = ok ? pages(j / p.page_size) : -1;
-    ok = ok && page >= 0;
-    const __nv_bfloat16* src = is_v ? p.vcache : p.kcache;
-    if (ok)
-      src += is_v ? (long long)page * p.v_page_stride + (long long)vh * p.v_head_stride + (long long)(j % p.page_size) * VD + c * 8
-                  : (long long)page * p.k_page_stride + (long long)kh * p.k_head_stride + (long long)(j % p.page_size) * KD + c * 8;
-    cp_async16(is_v ? v_dst + r * LDV + c * 8 : k_dst + r * LDK + c * 8, src, ok);
+  const int warp = tid >> 5, lane = tid & 31;
+  const bool is_v = warp >= 2;                 // warp-uniform
+  const int row = (warp & 1) * 32 + lane;      // the key or value row of this lane
+  const int j = j0 + row;
+  bool ok = j >= j_begin && j <= j_end;
+  const int page = ok ? pages(j / p.page_size) : -1;
+  ok = ok && page >= 0;
+  const __nv_bfloat16* src = is_v ? p.vcache : p.kcache;
+  if (ok)
+    src += is_v ? (long long)page * p.v_page_stride + (long long)vh * p.v_head_stride + (long long)(j % p.page_size) * VD
+                : (long long)page * p.k_page_stride + (long long)kh * p.k_head_stride + (long long)(j % p.page_size) * KD;
+  if (!is_v) {
+    constexpr int C = KD / 8;
+    __nv_bfloat16* dst = k_dst + (warp & 1) * 32 * LDK;
+#pragma unroll
+    for (int idx = lane; idx < 32 * C; idx += 32) {
+      const int r = idx / C, c = idx % C;
+      const unsigned long long a = __shfl_sync(0xffffffffu, (unsigned long long)src, r);
+      const int okr = __shfl_sync(0xffffffffu, (int)ok, r);
+      cp_async16(dst + r * LDK + c * 8, reinterpret_cast<const __nv_bfloat16*>(a) + (okr ? c * 8 : 0), okr != 0);
+    }
+  } else {
+    constexpr int C = VD / 8;
+    __nv_bfloat16* dst = v_dst + (warp & 1) * 32 * LDV;
+#pragma unroll
+    for (int idx = lane; idx < 32 * C; idx += 32) {
+      const int r = idx / C, c = idx % C;
+      const unsigned long long a = __shfl_sync(0xffffffffu, (unsigned long long)src, r);
+      const int okr = __shfl_sync(0xffffffffu, (int)ok, r);
+      cp_async16(dst + r * LDV + c * 8, reinterpret_cast<const __nv_bfloat16*>(a) + (okr ? c * 8 : 0), okr != 0);
+    }
   }
 }
 

@@ -343,7 +343,7 @@ __global__ void rope_pairs_kv_write_kernel(T* __restrict__ qkv, const int* __res
   const int t = blockIdx.x;
   if (t >= n_tokens) return;
   const float pos = (float)positions[t];
-  const int half_rot = rot_dims / 2, half_kd = kd / 2;
+  const int half_rot = rot_dims / 2, half_kd = (kd + 1) / 2;   // an odd key size ends in a value without a partner
   for (int i = threadIdx.x; i < half_rot; i += blockDim.x) {
     const float ang = __fmul_rn(pos, freq[i]);
     cs[i] = cosf(ang);
@@ -359,7 +359,8 @@ __global__ void rope_pairs_kv_write_kernel(T* __restrict__ qkv, const int* __res
   for (int idx = threadIdx.x; idx < (nq + nk) * half_kd; idx += blockDim.x) {
     const int h = idx / half_kd, i = idx % half_kd;
     const T* srcp = row + (size_t)h * kd + 2 * i;
-    const float u = to_f32(srcp[0]), v = to_f32(srcp[1]);
+    const bool pair = 2 * i + 1 < kd;
+    const float u = to_f32(srcp[0]), v = pair ? to_f32(srcp[1]) : 0.f;
     float ou = u, ov = v;
     if (i < half_rot) {
       const float c = cs[i], s = sn[i];
@@ -368,7 +369,7 @@ __global__ void rope_pairs_kv_write_kernel(T* __restrict__ qkv, const int* __res
     }
     T* dst = h < nq ? row + (size_t)h * kd + 2 * i : kbase + (long long)(h - nq) * k_head_stride + 2 * i;
     dst[0] = from_f32<T>(ou);
-    dst[1] = from_f32<T>(ov);
+    if (pair) dst[1] = from_f32<T>(ov);
   }
   const T* vsrc = row + (size_t)(nq + nk) * kd;
   for (int idx = threadIdx.x; idx < nv * vd; idx += blockDim.x) {
@@ -464,11 +465,11 @@ extern "C" int tllm_rope_pairs_kv_write(void* qkv, const int* positions, const f
                                         long long k_head_stride, long long v_page_stride, long long v_head_stride,
                                         int dtype, void* stream) {
   TLLM_REQUIRE(n_tokens > 0 && nq > 0 && nk > 0 && nv > 0 && vd > 0, "rope_pairs_kv_write: empty input");
-  TLLM_REQUIRE(kd > 0 && kd % 2 == 0, "rope_pairs_kv_write: key size %d must be even", kd);
+  TLLM_REQUIRE(kd > 0, "rope_pairs_kv_write: key size %d", kd);
   TLLM_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= kd && rot_dims <= 512 && (rot_dims == 0 || freq),
                "rope_pairs_kv_write: %d rotated values of %d (even, at most the key size and 512, with a frequency table)", rot_dims, kd);
   TLLM_REQUIRE(kcache && vcache && slot_mapping && page_size > 0, "rope_pairs_kv_write: needs cache pointers, a slot mapping and a page size");
-  const int work = (nq + nk) * kd / 2;
+  const int work = (nq + nk) * ((kd + 1) / 2);
   const int threads = work >= 512 ? 256 : 128;
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == TLLM_F32)

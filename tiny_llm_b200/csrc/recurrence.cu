@@ -19,14 +19,19 @@ TLLM_DEFINE_LAST_ERROR
 
 namespace tllm {
 
-__device__ __forceinline__ float sigmoid_f(float v) { return 1.f / (1.f + expf(-v)); }
+// The sigmoid in 32-bit.  For float32 activations it is the library's exponential and an IEEE division; for bfloat16
+// activations (whose inputs carry 8 bits) the hardware's exp2 and reciprocal approximations, 32-bit as well, good to
+// about 2^-21: a third of the instructions, and these kernels are bound by them.
+template <typename T> __device__ __forceinline__ float sigmoid_f(float v) { return 1.f / (1.f + expf(-v)); }
+template <> __device__ __forceinline__ float sigmoid_f<__nv_bfloat16>(float v) { return __frcp_rn(1.f + __expf(-v)); }
 
 struct Gate { float z, c; };
+template <typename T>
 __device__ __forceinline__ Gate min_gru_gate(float zl, float ul, float bz, float bu) {
   Gate g;
-  g.z = sigmoid_f(zl + bz);
+  g.z = sigmoid_f<T>(zl + bz);
   const float u = ul + bu;
-  g.c = u >= 0.f ? u + 0.5f : sigmoid_f(u);
+  g.c = u >= 0.f ? u + 0.5f : sigmoid_f<T>(u);
   return g;
 }
 __device__ __forceinline__ float min_gru_step(float s, const Gate& g) {
@@ -52,8 +57,8 @@ __device__ __forceinline__ float min_gru_walk(const T* __restrict__ zug, int ld,
 #pragma unroll
     for (int i = 0; i < AHEAD; ++i) {
       if (t + i < t1) {
-        s = min_gru_step(s, min_gru_gate(zl[i], ul[i], bz, bu));
-        if (Y) y[(size_t)(t + i) * width + c] = from_f32<T>(s * (gl[i] * sigmoid_f(gl[i])));
+        s = min_gru_step(s, min_gru_gate<T>(zl[i], ul[i], bz, bu));
+        if (Y) y[(size_t)(t + i) * width + c] = from_f32<T>(s * (gl[i] * sigmoid_f<T>(gl[i])));
       }
     }
   }
@@ -106,7 +111,7 @@ __global__ void min_gru_summary_kernel(const T* __restrict__ zug, int ld, const 
 #pragma unroll
     for (int i = 0; i < AHEAD; ++i) {
       if (t + i < t1) {
-        const Gate g = min_gru_gate(zl[i], ul[i], bz, bu);
+        const Gate g = min_gru_gate<T>(zl[i], ul[i], bz, bu);
         a = __fmul_rn(1.f - g.z, a);
         b = min_gru_step(b, g);
       }

@@ -222,7 +222,7 @@ def diff_combine(maps_out: torch.Tensor, lq1: torch.Tensor, lk1: torch.Tensor, l
 # Portions of at least this many tokens run the minGRU recurrence in segments (two kernels, every segment a thread
 # per channel) instead of one thread per channel walking the whole portion; 0 turns the segments off.  The 32-bit
 # path always walks serially: its results do not depend on how a sequence was cut into steps, to the bit.
-min_gru_segment = int(os.environ.get("TLLM_MINGRU_SEGMENT", "64"))
+min_gru_segment = int(os.environ.get("TLLM_MINGRU_SEGMENT", "32"))
 
 
 def min_gru_scan(zug: torch.Tensor, bias_z: torch.Tensor, bias_u: torch.Tensor, state: torch.Tensor,
@@ -454,9 +454,12 @@ def prefers_split(a: torch.Tensor, w: torch.Tensor) -> bool:
     return _tc_ok(a, w, None) and a.shape[0] <= 128 and _swap_splits(w.shape[0], a.shape[1], True) > 1
 
 
-def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
+def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool = False,
+           cluster_slices: bool = False) -> None:
     """out = a . w^T (w is [N, K], rows contiguous).  `out` may be of a's dtype or float32;
-    accumulate=True adds the product into a float32 `out`.  bfloat16 products run on the tensor
+    accumulate=True adds the product into a float32 `out`.  cluster_slices=True: a product of at most 128 rows
+    that stores bfloat16 cuts K into slices that meet in a thread-block cluster (every SM streams weights; without
+    it such a product has one CTA per 128 output columns, which walks all of K).  bfloat16 products run on the tensor
     cores (tcgen05) when K and the row stride of `a` are multiples of 8; float32 products, and
     the sizes TMA cannot take, run on the SIMT kernel."""
     _need_cuda(a, w, out)
@@ -482,7 +485,7 @@ def linear(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, accumulate: bool
         swap, splits = 0, 1
         if m <= 128:
             swap = 1
-            if (cluster_mask & 1) and mode in (OUT_ACC, OUT_SAME):
+            if ((cluster_mask & 1) and mode in (OUT_ACC, OUT_SAME)) or (cluster_slices and split_k and mode == OUT_SAME):
                 slices = _cluster_slices(n, k)
                 if slices > 1:   # the slices of K meet in a cluster: one writer per element, no atomics
                     _cluster_call(EPI_CL_ADD_F32 if mode == OUT_ACC else EPI_CL_BF16, a, w, out, slices)

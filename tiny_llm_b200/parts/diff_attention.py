@@ -93,7 +93,7 @@ class DiffAttention:
         t = h.shape[0]
         maps, nh, nkv, kd, vd = self.MAPS, self.num_heads, self.num_kv_heads, self.key_dim, self.value_dim
         qkv = ctx.workspace.get("qkv", (t, self.q_dim + self.k_dim + self.v_dim), ctx.dtype)
-        ops.linear(h, self.w_qkv, qkv)
+        ops.linear(h, self.w_qkv, qkv, cluster_slices=True)
         ops.rope_pairs_kv_write(qkv, ctx.batch.positions, self.freq, self.rot_dims, nh * maps, nkv * maps, nkv, kd, vd,
                                 cache.k, cache.v, cache.slot_mapping)
         per_map = ctx.workspace.get("attn_maps", (t, nh * maps * vd), torch.float32)

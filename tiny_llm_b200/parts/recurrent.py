@@ -48,7 +48,7 @@ class MinGRU:
     def forward(self, ctx, h, resid, cache) -> None:
         t = h.shape[0]
         zug = ctx.workspace.get("gru_in", (t, 3 * self.width), ctx.dtype)
-        ops.linear(h, self.w_in, zug)
+        ops.linear(h, self.w_in, zug, cluster_slices=True)
         y = ctx.workspace.get("gru_out", (t, self.width), ctx.dtype)
         ops.min_gru_scan(zug, self.bias_z, self.bias_u, cache.state, ctx.batch, y, ctx.workspace)
         ops.linear(y, self.w_o, resid, accumulate=True)
