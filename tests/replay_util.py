@@ -32,7 +32,7 @@ def plain_logits(model_dir, reqs, dtype):
 
 
 def tolerance(ref, dtype, ref32=None):
-    """float32: the engine must match to 2e-5 on these small models (1e-4 is the contract at 1.1B size).
+    """float32: the engine must match to 2e-5 on these small models (1e-4 is what is asked at 1.1B size).
     bfloat16: the yardstick is the error that bfloat16 rounding itself causes in the plain
     implementation for this very request, max |plain(bfloat16 roundings) - plain(32-bit)|: the engine
     rounds at the same places, so it must agree with the rounded plain implementation at least as

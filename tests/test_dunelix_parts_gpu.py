@@ -291,3 +291,23 @@ def test_differential_combine(dtype):
         ref = (o / torch.sqrt((o * o).mean(dim=-1, keepdim=True) + eps) * (1.0 - diff)).reshape(t, heads * vd)
         tol = 1e-5 if dtype == torch.float32 else 2.0 ** -8 * float(ref.abs().max())
         assert float((out.float().cpu() - ref).abs().max()) <= tol
+
+
+@pytest.mark.parametrize("m,n,k", [(8, 768, 1024), (3, 1000, 2048), (64, 6144, 512)])
+def test_input_projection_of_few_rows_with_k_slices_in_a_cluster(m, n, k):
+    """What the mixers' input projections ask for at decode: a bfloat16 product of few rows whose K slices meet in a
+    thread-block cluster (one writer per element: two runs give the same bits)."""
+    from tiny_llm_b200 import ops
+    g = torch.Generator().manual_seed(9)
+    a = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(n, k, generator=g) / k ** 0.5).to(torch.bfloat16)
+    assert ops._cluster_slices(n, k) > 1
+    ref = a.double() @ w.double().T
+    outs = []
+    for _ in range(2):
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=DEV)
+        ops.linear(a.to(DEV), w.to(DEV), out, cluster_slices=True)
+        outs.append(out.float().cpu())
+    assert float((outs[0] - ref.float()).abs().max()) <= 2.0 ** -8 * float(ref.abs().max())
+    assert torch.equal(outs[0], outs[1])
+    ops.check_status()

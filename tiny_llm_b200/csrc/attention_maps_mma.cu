@@ -92,7 +92,7 @@ __device__ __forceinline__ void load_tile(__nv_bfloat16* k_dst, __nv_bfloat16* v
 }
 
 template <int STAGES>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, (VD <= 128 ? 3 : 1))
 attention_maps_kernel(const MapsParams p) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
   __nv_bfloat16* q_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);
