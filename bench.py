@@ -10,7 +10,11 @@ and out every step.  Every figure is the median of REPEATS timed regions of K st
 one run.  The line also carries a 2,048-token prefill, decoding at batch 1 and 64, the stated workload
 of the model's benchmark (512-token prompts + 256 generated tokens through the entry point, admission and
 prompts included), the same points at the Llama-2-7B and Llama-3-8B layer sizes (all 32 layers), the HBM
-roofline of every decode point, and the clocks seen while timing."""
+roofline of every decode point, and the clocks seen while timing.
+
+`--design dunelix` measures another registered design instead (its own line, no record): prefill and decode of a
+Dunelix model at the TinyLlama layer sizes beside the Llama decoder at equal sizes, and its kernels alone beside their
+like kernels, each against its roofline (`--only decode` with it: the decode points alone)."""
 import argparse
 import json
 import os
@@ -548,7 +552,7 @@ def design_run(args, dtype, device, pk):
                        "32 heads of 64, 4 key/value heads, equal width, feed-forward, layers and vocabulary",
               "l2": "whole steps: weights larger than L2; kernels alone: L2 flushed before every timed call"}
     sampler = ClockSampler().start()
-    for label in ("dunelix", "llama"):
+    for label in ("dunelix", "llama")[:1 if args.only == "decode" else 2]:
         if label == "dunelix":
             cfg, model = build_design(dunelix_shape(), dtype, device)
         else:
@@ -556,7 +560,7 @@ def design_run(args, dtype, device, pk):
         runner = make_runner(model, dtype, device, max_tokens=64 * CONTEXT, page_size=PAGE, max_requests=64,
                              max_tokens_per_step=2048, max_positions=CONTEXT)
         rec = {}
-        for tt in (512, 2048):
+        for tt in (512, 2048) if args.only != "decode" else ():
             ms = timed_prefill(runner, tt, repeats=3)
             rec[f"prefill_{tt}"] = {"ms": round(ms, 3), "tokens_per_s": round(tt * 1e3 / ms, 1)}
         for bsz in (8, 64):
@@ -570,7 +574,7 @@ def design_run(args, dtype, device, pk):
         gc.collect()
         torch.cuda.empty_cache()
     result["clocks"] = sampler.stop()
-    if dtype == torch.bfloat16:
+    if dtype == torch.bfloat16 and args.only == "all":
         result["kernels"] = design_kernels(dtype, device, pk)
     ops.check_status()
     print(json.dumps(result))

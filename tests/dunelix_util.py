@@ -119,5 +119,6 @@ def compare(got, ref, prefix, tol, what):
                                  f"{int(bad[0])} of {r.shape[0]} (max |diff| {float(diff.max()):.3e}, tolerance "
                                  f"{tol[rid]:.3e}; wrong positions: {bad.tolist()[:20]})")
         worst = max(worst, float(diff.max()) / tol[rid])
-    print(f"[margin] {what}: worst |diff| / tolerance = {worst:.3g}")
+    import replay_util
+    replay_util.record_margin(what, "", worst)   # printed, and appended to the file TLLM_MARGIN_FILE names
     return worst

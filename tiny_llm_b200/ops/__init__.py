@@ -97,7 +97,7 @@ def replay_tape(tape) -> None:
 def knobs():
     """The module's switches that decide which kernels a step launches; a tape or graph holds for one setting of them."""
     return (force_generic, split_k, cluster_mask, attention_tc, decode_wide_ctas, decode_cluster_merge, qkv_fused_rows,
-            linear_skinny, generic_attention_split, split_mixed_attention, min_gru_segment, attention_maps_tc, _pdl)
+            linear_skinny, generic_attention_split, split_mixed_attention, min_gru_segment, attention_maps_tc, attention_maps_decode_pairs, _pdl)
 
 
 def _i32(t: Optional[torch.Tensor], name: str):
@@ -685,6 +685,12 @@ def paged_attention(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_d
 attention_maps_tc = os.environ.get("TLLM_ATTENTION_MAPS_TC", "1") != "0"
 
 
+# Decoded tokens alone in a step, up to this many (token, head, map) pairs: the CUDA-core kernel, which gives eight
+# warps to every pair and so walks a pair's keys eight tiles at a time, instead of the tensor-core kernel, whose one
+# CTA per (request, key row) walks them tile after tile (0: always the tensor-core kernel; a switch for measurements).
+attention_maps_decode_pairs = int(os.environ.get("TLLM_ATTENTION_MAPS_DECODE_PAIRS", "0"))
+
+
 def paged_attention_maps(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, maps: int, key_dim: int, value_dim: int,
                          k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor, batch,
                          out: torch.Tensor, scale: float, window: Optional[int] = None,
@@ -706,8 +712,9 @@ def paged_attention_maps(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, m
             k_cache.shape[3] != key_dim or v_cache.stride(3) != 1 or v_cache.stride(2) != value_dim or \
             v_cache.shape[1] != num_kv_heads or v_cache.shape[3] != value_dim or k_cache.shape[2] != v_cache.shape[2]:
         raise KernelError("paged_attention_maps: shapes or dtypes do not fit")
+    few = getattr(batch, "max_q_len", 0) == 1 and t * num_heads * maps <= attention_maps_decode_pairs
     if qkv.dtype == torch.bfloat16 and out.dtype == torch.float32 and not force_generic and attention_maps_tc and \
-            key_dim % 16 == 0 and value_dim % 16 == 0 and 16 <= key_dim <= 256 and 16 <= value_dim <= 256 and \
+            not few and key_dim % 16 == 0 and value_dim % 16 == 0 and 16 <= key_dim <= 256 and 16 <= value_dim <= 256 and \
             qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0:
         # bfloat16: the tensor-core kernel compiled for this pair of sizes (prompt portions and decoded tokens alike)
         lib = build.load_library("attention_maps_mma", flags=(f"-DTLLM_HEAD_DIM={key_dim}", f"-DTLLM_VALUE_DIM={value_dim}"))
