@@ -714,7 +714,7 @@ def paged_attention_maps(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, m
         raise KernelError("paged_attention_maps: shapes or dtypes do not fit")
     few = getattr(batch, "max_q_len", 0) == 1 and t * num_heads * maps <= attention_maps_decode_pairs
     if qkv.dtype == torch.bfloat16 and out.dtype == torch.float32 and not force_generic and attention_maps_tc and \
-            not few and key_dim % 16 == 0 and value_dim % 16 == 0 and 16 <= key_dim <= 256 and 16 <= value_dim <= 256 and \
+            not few and scale > 0 and key_dim % 16 == 0 and value_dim % 16 == 0 and 16 <= key_dim <= 256 and 16 <= value_dim <= 256 and \
             qkv.stride(0) % 8 == 0 and qkv.data_ptr() % 16 == 0:
         # bfloat16: the tensor-core kernel compiled for this pair of sizes (prompt portions and decoded tokens alike)
         lib = build.load_library("attention_maps_mma", flags=(f"-DTLLM_HEAD_DIM={key_dim}", f"-DTLLM_VALUE_DIM={value_dim}"))
