@@ -42,7 +42,7 @@ DUNE_B = {
     "architecture": "Dunelix", "vocab": 331, "width": 96, "residual_mult": 1.0, "norm": {"eps": 1e-6},
     "initializer_range": 0.08,
     "layers": [
-        with_mlp(attention(3, 1, 24, 56, 0.35, 0.5, mask=64, rot={"dims": 24, "base": 5000.0}), 136),
+        with_mlp(attention(3, 1, 32, 48, 0.3, 0.5, mask=64, rot={"dims": 32, "base": 5000.0}), 136),   # sizes the tensor-core kernel takes
         with_mlp(gru(128), 104),
         with_mlp(gru(72), 88),
     ],
