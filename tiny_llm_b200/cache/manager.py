@@ -9,7 +9,9 @@ request has one block table per group, whatever the number of layers.
 
 Groups.  A mixer declares its need (`KVNeed`: heads, head size, optional window; `StateNeed`: a
 fixed shape per request).  Calls with the same KVNeed form one group with its own pool, sized for
-the same number of tokens.  A group with a window gives a page back as soon as every position in it
+the same number of tokens.  A mixer that keeps several things per request (keys and values, summaries
+of blocks of keys, a recurrent state) declares a tuple of needs and gets a tuple of views in the same
+order.  A group with a window gives a page back as soon as every position in it
 lies before the window of the request's next token; its block-table entry becomes -1 and the
 attention kernels never look there.  A group whose keys are visible inside a chunk of positions only
 does the same with the pages that lie wholly before the chunk of the request's next token.
@@ -34,6 +36,9 @@ class KVNeed:
     value_dim: Optional[int] = None  # size of a value row when it differs from the key's head_dim
     key_rows: int = 1  # key rows per key/value head and token (a mixer with several score maps over the same values)
     chunk: Optional[int] = None  # n: a token sees keys of its own chunk of n positions only (counted from position 0)
+    # n > 1: the entry holds one row per block of n positions (a summary of the block, written when the block's
+    # last position arrives), so a request of t tokens holds t // n rows; such an entry never gives pages back
+    stride: int = 1
 
     @property
     def v_dim(self) -> int:
@@ -93,10 +98,11 @@ class KVGroup:
 
     def bytes_per_token(self, itemsize: int) -> int:
         n = self.need
-        return self.num_entries * n.num_kv_heads * (n.key_rows * n.head_dim + n.v_dim) * itemsize
+        return self.num_entries * n.num_kv_heads * (n.key_rows * n.head_dim + n.v_dim) * itemsize // n.stride
 
     def pages_for(self, tokens: int) -> int:
-        return -(-tokens // self.page_size)
+        """Pages a request of `tokens` tokens holds: one row per token, or per complete block of `stride` tokens."""
+        return -(-(tokens // self.need.stride) // self.page_size)
 
     def first_needed_page(self, next_pos: int) -> int:
         """Index of the first page that the token at `next_pos` can still see."""
@@ -170,25 +176,34 @@ class CacheManager:
         self.refs: List[CacheEntryRef] = []
         by_need: Dict[KVNeed, int] = {}
         counts: Dict[KVNeed, int] = {}
+
+        def flat(need):
+            return need if isinstance(need, (tuple, list)) else (need,)
         for need in needs:
-            if isinstance(need, KVNeed):
-                counts[need] = counts.get(need, 0) + 1
+            for one in flat(need):
+                if isinstance(one, KVNeed):
+                    if one.stride < 1 or (one.stride > 1 and one.bounded):
+                        raise ValueError("a strided cache entry holds every block: it has neither window nor chunk")
+                    counts[one] = counts.get(one, 0) + 1
         num_pages = -(-max_tokens // page_size)
+        taken: Dict[KVNeed, int] = {}
+
+        def ref_for(one) -> CacheEntryRef:
+            if isinstance(one, KVNeed):
+                if one not in by_need:
+                    by_need[one] = len(self.groups)
+                    self.groups.append(KVGroup(one, counts[one], num_pages, page_size))
+                    taken[one] = 0
+                taken[one] += 1
+                return CacheEntryRef(group=by_need[one], entry=taken[one] - 1)
+            if isinstance(one, StateNeed):
+                return CacheEntryRef(state=self.slots.register(one))
+            if one is None:
+                return CacheEntryRef()
+            raise TypeError(f"unknown cache need {one!r}")
         for need in needs:
-            if isinstance(need, KVNeed):
-                if need not in by_need:
-                    by_need[need] = len(self.groups)
-                    self.groups.append(KVGroup(need, counts[need], num_pages, page_size))
-                    counts[need] = 0
-                g = by_need[need]
-                self.refs.append(CacheEntryRef(group=g, entry=counts[need]))
-                counts[need] += 1
-            elif isinstance(need, StateNeed):
-                self.refs.append(CacheEntryRef(state=self.slots.register(need)))
-            elif need is None:
-                self.refs.append(CacheEntryRef())
-            else:
-                raise TypeError(f"unknown cache need {need!r}")
+            # a mixer with several needs (a tuple) gets a tuple of references, one per need, in the same order
+            self.refs.append(tuple(ref_for(one) for one in need) if isinstance(need, (tuple, list)) else ref_for(need))
         self.kv_len: Dict[Hashable, int] = {}
         self._reserved: Dict[Hashable, int] = {}
         self.birth: Dict[Hashable, int] = {}   # a number that differs between two lives of the same request id

@@ -4,7 +4,8 @@ from .registry import (config_class_for, config_from_dict, load_config, register
 from .spec import LayerCall, LayerSpec, ModelSpec, PartSpec
 from .llama import LlamaConfig
 from .dunelix import DunelixConfig
+from .zozenex import ZozenexConfig
 
-__all__ = ["ConfigError", "LlamaConfig", "DunelixConfig", "LayerCall", "LayerSpec", "ModelSpec", "PartSpec",
+__all__ = ["ConfigError", "LlamaConfig", "DunelixConfig", "ZozenexConfig", "LayerCall", "LayerSpec", "ModelSpec", "PartSpec",
            "config_class_for", "config_from_dict", "load_config", "register_architecture",
            "registered_architectures"]

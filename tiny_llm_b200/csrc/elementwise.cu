@@ -46,6 +46,30 @@ __global__ void rms_norm_kernel(const float* __restrict__ x, const float* __rest
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = from_f32<T>((w[i] * src[i]) * inv);
 }
 
+// resid_j += scale * w_j * x_j / sqrt(sum_j(x_j^2)/H + eps): a branch that is normed before it joins the stream.
+// clear != 0: x is handed back zeroed (a branch buffer that products accumulate into).
+__global__ void rms_norm_add_kernel(float* __restrict__ x, const float* __restrict__ w, float* __restrict__ resid,
+                                    int n_rows, int hidden, float eps, float scale, int clear) {
+  __shared__ float scratch[33];
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x;
+  if (r >= n_rows) return;
+  float* src = x + (size_t)r * hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    const float v = src[i];
+    ss += v * v;
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = 1.f / sqrtf(ss / (float)hidden + eps);
+  float* dst = resid + (size_t)r * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    dst[i] += scale * ((w[i] * src[i]) * inv);
+    if (clear) src[i] = 0.f;
+  }
+}
+
 __device__ __forceinline__ void store4(float* p, float a, float b, float c, float d) {
   *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
 }
@@ -543,6 +567,14 @@ extern "C" int tllm_rms_norm(const float* x, const float* w, void* out, const in
     TLLM_LAUNCH("rms_norm", rms_norm_kernel<float>, n_rows, threads, 0, s, x, w, (float*)out, rows, n_rows, hidden, eps);
   else
     TLLM_LAUNCH("rms_norm", rms_norm_kernel<__nv_bfloat16>, n_rows, threads, 0, s, x, w, (__nv_bfloat16*)out, rows, n_rows, hidden, eps);
+  return TLLM_OK;
+}
+
+extern "C" int tllm_rms_norm_add(float* x, const float* w, float* resid, int n_rows, int hidden, float eps, float scale,
+                                 int clear, void* stream) {
+  TLLM_REQUIRE(n_rows > 0 && hidden > 0, "rms_norm_add: empty input");
+  const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  TLLM_LAUNCH("rms_norm_add", rms_norm_add_kernel, n_rows, threads, 0, (cudaStream_t)stream, x, w, resid, n_rows, hidden, eps, scale, clear);
   return TLLM_OK;
 }
 

@@ -93,6 +93,11 @@ class StepContext:
 
     def cache_view(self, order_pos: int):
         ref = self.runner.cache.refs[order_pos]
+        if isinstance(ref, tuple):   # a mixer with several needs gets one view per need
+            return tuple(self._view(one) for one in ref)
+        return self._view(ref)
+
+    def _view(self, ref):
         if ref.group is not None:
             g = self.runner.cache.groups[ref.group]
             m = self.batch.groups[ref.group]
@@ -245,6 +250,16 @@ class ModelRunner:
                 bt[i, :nb] = table
                 bt[i, nb:] = -1
                 p = np.arange(s, s + n)
+                if g.need.stride > 1:
+                    # one row per block of `stride` positions: the token that completes a block names the block's
+                    # row, every other token of the step -1
+                    done = (p + 1) % g.need.stride == 0
+                    blocks = p[done] // g.need.stride
+                    sm[cur: cur + n] = -1
+                    sm[cur: cur + n][done] = np.asarray(table, dtype=np.int64)[blocks // g.page_size] * g.page_size \
+                        + blocks % g.page_size
+                    cur += n
+                    continue
                 pages = np.asarray(table, dtype=np.int64)[p // g.page_size]
                 if (pages < 0).any():
                     raise RuntimeError(f"request {e.rid!r} writes into a page it has given back")
@@ -349,6 +364,14 @@ class ModelRunner:
                     bt[i, len(table):] = -1
                 else:
                     bt[i] = self._table_row(gi, e.rid, table)
+            if g.need.stride > 1:   # a row per block of positions: only a token that completes a block writes one
+                done = (starts_np + 1) % g.need.stride == 0
+                rows = starts_np // g.need.stride
+                sm[:] = -1
+                if done.any():
+                    sm[done] = bt[np.arange(r)[done], rows[done] // g.page_size].astype(np.int64) * g.page_size \
+                        + rows[done] % g.page_size
+                continue
             blocks = starts_np // g.page_size
             pages = bt[np.arange(r), blocks].astype(np.int64)
             if (pages < 0).any():

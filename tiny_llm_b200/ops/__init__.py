@@ -97,7 +97,7 @@ def replay_tape(tape) -> None:
 def knobs():
     """The module's switches that decide which kernels a step launches; a tape or graph holds for one setting of them."""
     return (force_generic, split_k, cluster_mask, attention_tc, decode_wide_ctas, decode_cluster_merge, qkv_fused_rows,
-            linear_skinny, generic_attention_split, split_mixed_attention, min_gru_segment, attention_maps_tc, attention_maps_decode_pairs, _pdl)
+            linear_skinny, generic_attention_split, split_mixed_attention, min_gru_segment, linear_attention_segment, attention_maps_tc, attention_maps_decode_pairs, _pdl)
 
 
 def _i32(t: Optional[torch.Tensor], name: str):
@@ -296,6 +296,271 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, cos: Optional[torc
         qkv.stride(0), _ptr(k_cache if slot_mapping is not None else None),
         _ptr(v_cache if slot_mapping is not None else None), _ptr(slot_mapping), page_size,
         ctypes.c_longlong(page_stride), ctypes.c_longlong(head_stride), _code(qkv.dtype), _stream())
+
+
+# ----------------------------------------------------------------------------- linear attention, windows, experts
+
+
+def rms_norm_add(x: torch.Tensor, weight: torch.Tensor, eps: float, scale: float, resid: torch.Tensor,
+                 clear: bool = True) -> None:
+    """resid += scale * weight * x / sqrt(mean(x^2) + eps), row by row, all float32; clear=True hands `x` back zeroed
+    (a branch buffer that products accumulate into)."""
+    _need_cuda(x, weight, resid)
+    if x.dtype != torch.float32 or resid.dtype != torch.float32 or weight.dtype != torch.float32 or x.shape != resid.shape \
+            or not x.is_contiguous() or not resid.is_contiguous() or weight.numel() != x.shape[1]:
+        raise KernelError("rms_norm_add: shapes or dtypes do not fit")
+    lib = build.load_library("elementwise")
+    _call(lib, lib.tllm_rms_norm_add, _ptr(x), _ptr(weight), _ptr(resid), x.shape[0], x.shape[1], ctypes.c_float(eps),
+          ctypes.c_float(scale), 1 if clear else 0, _stream())
+
+
+# Portions of at least twice this many tokens run the linear-attention recurrence in segments (bfloat16 only: the
+# 32-bit path always walks a request's tokens in order, so that its state has the same bits however it was cut); 0: never.
+linear_attention_segment = int(os.environ.get("TLLM_LINEAR_ATTENTION_SEGMENT", "128"))
+
+
+def linear_attention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, heads: int, key_dim: int, value_dim: int,
+                          state: torch.Tensor, batch, out: torch.Tensor, q_scale: float = 1.0, k_scale: float = 1.0,
+                          head_decay: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+                          gate_bias: Optional[torch.Tensor] = None, inv_tau: float = 1.0, workspace=None) -> None:
+    """S_t = diag(a_t) S_(t-1) + (k_scale k_t) v_t^T, out_t = S_t^T (q_scale q_t) per head, over the step's tokens.
+    q, k [T, heads * key_dim], v [T, heads * value_dim] (row slices of a projection are fine); out float32
+    [T, heads * value_dim]; state float32 [slots, heads, key_dim, value_dim], carried from step to step.
+    a_t is `head_decay[h]` (float32 [heads]) for every channel, or sigmoid(gate + gate_bias)^inv_tau per key
+    channel with `gate` float32 [T, heads * key_dim]."""
+    _need_cuda(q, k, v, state, out, head_decay, gate, gate_bias)
+    t = q.shape[0]
+    if q.shape != (t, heads * key_dim) or k.shape != q.shape or v.shape != (t, heads * value_dim) or \
+            q.dtype != k.dtype or q.dtype != v.dtype or any(x.stride(1) != 1 for x in (q, k, v)) or \
+            out.shape != (t, heads * value_dim) or out.dtype != torch.float32 or not out.is_contiguous() or \
+            state.dtype != torch.float32 or not state.is_contiguous() or tuple(state.shape[1:]) != (heads, key_dim, value_dim):
+        raise KernelError("linear_attention_scan: shapes or dtypes do not fit")
+    if (head_decay is None) == (gate is None):
+        raise KernelError("linear_attention_scan: give a decay per head or a gate, not both")
+    if head_decay is not None and (head_decay.dtype != torch.float32 or head_decay.numel() != heads):
+        raise KernelError("linear_attention_scan: one float32 decay per head")
+    if gate is not None and (gate.dtype != torch.float32 or gate.shape != q.shape or gate.stride(1) != 1 or gate_bias is None or
+                             gate_bias.dtype != torch.float32 or gate_bias.numel() != heads * key_dim):
+        raise KernelError("linear_attention_scan: the gate and its bias do not fit")
+    seg, summary = 0, None
+    if q.dtype == torch.bfloat16 and workspace is not None and linear_attention_segment > 0 and \
+            batch.max_q_len >= 2 * linear_attention_segment:
+        seg = linear_attention_segment
+        segs = -(-batch.max_q_len // seg)
+        per = heads * (key_dim * value_dim + key_dim)
+        summary = workspace.get("lin_attn_summary", (batch.num_requests * (segs * per + heads * key_dim * value_dim),),
+                                torch.float32)
+    lib = build.load_library("linear_attention")
+    _call(lib, lib.tllm_linear_attention_scan, _ptr(q), _ptr(k), _ptr(v), q.stride(0), k.stride(0), v.stride(0),
+          _ptr(head_decay), _ptr(gate), 0 if gate is None else gate.stride(0), _ptr(gate_bias), ctypes.c_float(inv_tau),
+          ctypes.c_float(q_scale), ctypes.c_float(k_scale), _ptr(state), _ptr(batch.slots), _ptr(batch.cu_q), _ptr(out),
+          heads, key_dim, value_dim, batch.num_requests, batch.max_q_len, seg, _ptr(summary), _code(q.dtype), _stream())
+
+
+def head_norm_gate(o: torch.Tensor, weight: Optional[torch.Tensor], gate: torch.Tensor, heads: int, value_dim: int,
+                   eps: float, out: torch.Tensor) -> None:
+    """out[t, h] = o[t, h] / sqrt(mean(o[t, h]^2) + eps) * weight * silu(gate[t, h]) per (token, head); o float32
+    [T, heads * value_dim], weight float32 [value_dim] or None, gate and out [T, heads * value_dim] in the engine's dtype."""
+    _need_cuda(o, weight, gate, out)
+    t = o.shape[0]
+    if o.dtype != torch.float32 or not o.is_contiguous() or o.shape != (t, heads * value_dim) or gate.shape != o.shape or \
+            gate.stride(1) != 1 or out.shape != o.shape or not out.is_contiguous() or out.dtype != gate.dtype or \
+            (weight is not None and (weight.dtype != torch.float32 or weight.numel() != value_dim)):
+        raise KernelError("head_norm_gate: shapes or dtypes do not fit")
+    lib = build.load_library("linear_attention")
+    _call(lib, lib.tllm_head_norm_gate, _ptr(o), _ptr(weight), _ptr(gate), gate.stride(0), heads, value_dim,
+          ctypes.c_float(eps), _ptr(out), ctypes.c_longlong(t * heads), _code(out.dtype), _stream())
+
+
+def _paged(name: str, c: torch.Tensor, rows: int, dim: int) -> None:
+    if c.dim() != 4 or c.shape[1] != rows or c.shape[3] != dim or c.stride(3) != 1 or c.stride(2) != dim:
+        raise KernelError(f"{name}: cache layout does not fit (wanted [pages, {rows}, page_size, {dim}])")
+
+
+def rope_halves_kv_write(qkv: torch.Tensor, positions: torch.Tensor, freq_k: Optional[torch.Tensor], rot_dims: int,
+                         freq_v: Optional[torch.Tensor], num_q_rows: int, num_k_rows: int, num_v_rows: int, key_dim: int,
+                         value_dim: int, k_cache: torch.Tensor, v_cache: torch.Tensor, slot_mapping: torch.Tensor) -> None:
+    """Rows of `qkv`: query rows and key rows of key_dim values, then value rows of value_dim values.  The first
+    rot_dims values of every query and key row are rotated (value i with value i + rot_dims / 2) by
+    positions[t] * freq_k[i]; with `freq_v` the value rows are rotated over their whole size (value m with
+    m + value_dim / 2) by positions[t] * freq_v[m].  Queries are rewritten in place, keys and values go to their pages."""
+    _need_cuda(qkv, positions, freq_k, freq_v, k_cache, v_cache, slot_mapping)
+    _i32(positions, "positions")
+    _i32(slot_mapping, "slot_mapping")
+    t, width = qkv.shape
+    if width != (num_q_rows + num_k_rows) * key_dim + num_v_rows * value_dim or qkv.stride(1) != 1:
+        raise KernelError("rope_halves_kv_write: the rows of qkv do not fit")
+    _paged("rope_halves_kv_write", k_cache, num_k_rows, key_dim)
+    _paged("rope_halves_kv_write", v_cache, num_v_rows, value_dim)
+    if k_cache.dtype != qkv.dtype or v_cache.dtype != qkv.dtype or k_cache.shape[2] != v_cache.shape[2]:
+        raise KernelError("rope_halves_kv_write: cache dtype or page size does not fit")
+    for f, n in ((freq_k if rot_dims else None, rot_dims), (freq_v, value_dim)):
+        if f is not None and (f.dtype != torch.float32 or not f.is_contiguous() or f.numel() * 2 != n):
+            raise KernelError("rope_halves_kv_write: a frequency table does not fit")
+    lib = build.load_library("window_attention")
+    _call(lib, lib.tllm_rope_halves_kv_write, _ptr(qkv), _ptr(positions), _ptr(freq_k if rot_dims else None), rot_dims,
+          _ptr(freq_v), t, num_q_rows, num_k_rows, num_v_rows, key_dim, value_dim, qkv.stride(0), _ptr(k_cache), _ptr(v_cache),
+          _ptr(slot_mapping), k_cache.shape[2], ctypes.c_longlong(k_cache.stride(0)), ctypes.c_longlong(k_cache.stride(1)),
+          ctypes.c_longlong(v_cache.stride(0)), ctypes.c_longlong(v_cache.stride(1)), _code(qkv.dtype), _stream())
+
+
+def pool_kv_blocks(k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor, pool_k: torch.Tensor,
+                   pool_v: torch.Tensor, pool_slots: torch.Tensor, batch, pool: int) -> None:
+    """Every token of the step whose entry of `pool_slots` is not negative completes a block of `pool` positions: the
+    means of the block's cached keys and values (32-bit sums in the order of the positions) are written to that row
+    of pool_k / pool_v."""
+    _need_cuda(k_cache, v_cache, block_table, pool_k, pool_v, pool_slots)
+    _i32(block_table, "block_table")
+    _i32(pool_slots, "pool_slots")
+    nkv, kd, vd = k_cache.shape[1], k_cache.shape[3], v_cache.shape[3]
+    for name, c, d in (("k", k_cache, kd), ("v", v_cache, vd), ("pool k", pool_k, kd), ("pool v", pool_v, vd)):
+        _paged("pool_kv_blocks", c, nkv, d)
+    if len({c.dtype for c in (k_cache, v_cache, pool_k, pool_v)}) != 1 or len({c.shape[2] for c in (k_cache, v_cache, pool_k, pool_v)}) != 1:
+        raise KernelError("pool_kv_blocks: the caches differ in dtype or page size")
+    lib = build.load_library("window_attention")
+    ll = ctypes.c_longlong
+    _call(lib, lib.tllm_pool_kv_blocks, _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(pool_k),
+          _ptr(pool_v), _ptr(pool_slots), _ptr(batch.positions), _ptr(batch.token_request), batch.num_tokens, nkv, pool, kd, vd,
+          k_cache.shape[2], ll(k_cache.stride(0)), ll(k_cache.stride(1)), ll(v_cache.stride(0)), ll(v_cache.stride(1)),
+          ll(pool_k.stride(0)), ll(pool_k.stride(1)), ll(pool_v.stride(0)), ll(pool_v.stride(1)), _code(k_cache.dtype), _stream())
+
+
+class _WinArgs(ctypes.Structure):
+    _fields_ = [("qkv", ctypes.c_void_p), ("row_stride", ctypes.c_int), ("nh", ctypes.c_int), ("nkv", ctypes.c_int),
+                ("kd", ctypes.c_int), ("vd", ctypes.c_int), ("k", ctypes.c_void_p), ("v", ctypes.c_void_p),
+                ("table", ctypes.c_void_p), ("max_blocks", ctypes.c_int),
+                ("k_page_stride", ctypes.c_longlong), ("k_head_stride", ctypes.c_longlong),
+                ("v_page_stride", ctypes.c_longlong), ("v_head_stride", ctypes.c_longlong),
+                ("pk", ctypes.c_void_p), ("pv", ctypes.c_void_p), ("ptable", ctypes.c_void_p), ("pmax_blocks", ctypes.c_int),
+                ("pk_page_stride", ctypes.c_longlong), ("pk_head_stride", ctypes.c_longlong),
+                ("pv_page_stride", ctypes.c_longlong), ("pv_head_stride", ctypes.c_longlong),
+                ("page_size", ctypes.c_int), ("positions", ctypes.c_void_p), ("token_request", ctypes.c_void_p),
+                ("out", ctypes.c_void_p), ("scale", ctypes.c_float), ("cap", ctypes.c_float), ("head_bias", ctypes.c_void_p),
+                ("window", ctypes.c_int), ("pool", ctypes.c_int), ("fv", ctypes.c_void_p), ("n_tokens", ctypes.c_int)]
+
+
+def window_pool_attention(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int,
+                          k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+                          pool_k: Optional[torch.Tensor], pool_v: Optional[torch.Tensor],
+                          pool_table: Optional[torch.Tensor], batch, out: torch.Tensor, scale: float,
+                          softcap: Optional[float], head_bias: torch.Tensor, window: Optional[int], pool: Optional[int],
+                          freq_v: Optional[torch.Tensor]) -> None:
+    """Attention without softmax: out[t, h] = sum over visible keys of sigmoid(cap(q . k * scale) + head_bias[h]) * v,
+    cap(s) = softcap * tanh(s / softcap) (None: s).  Visible to position i: tokens j with 0 <= i - j < window (None:
+    all j <= i) and, with `pool`, the block rows b of pool_k / pool_v with b * pool + pool - 1 <= i - window.  With
+    `freq_v` the head's output is turned back by the query's position (value m with m + value_dim / 2, angle
+    -i * freq_v[m]).  The queries are the first num_heads * key_dim values of every row of `qkv`."""
+    _need_cuda(qkv, k_cache, v_cache, block_table, pool_k, pool_v, pool_table, out, head_bias, freq_v)
+    _i32(block_table, "block_table")
+    _i32(pool_table, "pool_table")
+    t = qkv.shape[0]
+    _paged("window_pool_attention", k_cache, num_kv_heads, key_dim)
+    _paged("window_pool_attention", v_cache, num_kv_heads, value_dim)
+    if qkv.stride(1) != 1 or qkv.shape[1] < num_heads * key_dim or out.shape != (t, num_heads * value_dim) or \
+            not out.is_contiguous() or out.dtype != qkv.dtype or k_cache.dtype != qkv.dtype or v_cache.dtype != qkv.dtype or \
+            head_bias.dtype != torch.float32 or head_bias.numel() != num_heads or \
+            (freq_v is not None and (freq_v.dtype != torch.float32 or freq_v.numel() * 2 != value_dim)):
+        raise KernelError("window_pool_attention: shapes or dtypes do not fit")
+    a = _WinArgs()
+    a.qkv, a.row_stride, a.nh, a.nkv, a.kd, a.vd = qkv.data_ptr(), qkv.stride(0), num_heads, num_kv_heads, key_dim, value_dim
+    a.k, a.v, a.table, a.max_blocks = k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(), block_table.shape[1]
+    a.k_page_stride, a.k_head_stride = k_cache.stride(0), k_cache.stride(1)
+    a.v_page_stride, a.v_head_stride = v_cache.stride(0), v_cache.stride(1)
+    if pool:
+        if pool_k is None or pool_v is None or pool_table is None or window is None:
+            raise KernelError("window_pool_attention: pooled blocks need their cache, their table and a window")
+        _paged("window_pool_attention", pool_k, num_kv_heads, key_dim)
+        _paged("window_pool_attention", pool_v, num_kv_heads, value_dim)
+        if pool_k.dtype != qkv.dtype or pool_v.dtype != qkv.dtype or pool_k.shape[2] != k_cache.shape[2]:
+            raise KernelError("window_pool_attention: the block cache differs in dtype or page size")
+        a.pk, a.pv, a.ptable, a.pmax_blocks = pool_k.data_ptr(), pool_v.data_ptr(), pool_table.data_ptr(), pool_table.shape[1]
+        a.pk_page_stride, a.pk_head_stride = pool_k.stride(0), pool_k.stride(1)
+        a.pv_page_stride, a.pv_head_stride = pool_v.stride(0), pool_v.stride(1)
+    a.page_size = k_cache.shape[2]
+    a.positions, a.token_request, a.out = batch.positions.data_ptr(), batch.token_request.data_ptr(), out.data_ptr()
+    a.scale, a.cap, a.head_bias = scale, (softcap or 0.0), head_bias.data_ptr()
+    a.window, a.pool, a.fv, a.n_tokens = (window or 0), (pool or 0), (None if freq_v is None else freq_v.data_ptr()), t
+    lib = build.load_library("window_attention")
+    _call(lib, lib.tllm_window_pool_attention, ctypes.byref(a), _code(qkv.dtype), _stream())
+
+
+def gelu(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = 0.5 x (1 + erf(x / sqrt 2)) element by element (`out` may be `x`)."""
+    _need_cuda(x, out)
+    if x.shape != out.shape or x.dtype != out.dtype or not x.is_contiguous() or not out.is_contiguous():
+        raise KernelError("gelu: shapes or dtypes do not fit")
+    lib = build.load_library("moe")
+    _call(lib, lib.tllm_gelu, _ptr(x), _ptr(out), ctypes.c_longlong(x.numel()), _code(x.dtype), _stream())
+
+
+def moe_route(logits: torch.Tensor, num_experts: int, correction: torch.Tensor, scale: float, ids: torch.Tensor,
+              weights: torch.Tensor) -> None:
+    """Per token: s = sigmoid(logits[t, :num_experts]); ids[t] = the `top` experts with the largest s + correction (ties:
+    the lower index), weights[t] = their s * scale.  logits float32 (further columns are ignored), ids int32 [T, top],
+    weights float32 [T, top]."""
+    _need_cuda(logits, correction, ids, weights)
+    t, top = ids.shape
+    if logits.dtype != torch.float32 or logits.stride(1) != 1 or logits.shape[0] != t or logits.shape[1] < num_experts or \
+            correction.dtype != torch.float32 or correction.numel() != num_experts or ids.dtype != torch.int32 or \
+            weights.dtype != torch.float32 or weights.shape != ids.shape or not ids.is_contiguous() or not weights.is_contiguous():
+        raise KernelError("moe_route: shapes or dtypes do not fit")
+    lib = build.load_library("moe")
+    _call(lib, lib.tllm_moe_route, _ptr(logits), logits.stride(0), num_experts, _ptr(correction), ctypes.c_float(scale), top,
+          _ptr(ids), _ptr(weights), t, _stream())
+
+
+def moe_tile_rows(pairs: int, num_experts: int) -> int:
+    """Rows per tile of the grouped product: 16 while an expert gets few rows (decode), else 64."""
+    return 16 if pairs <= 16 * num_experts else 64
+
+
+def moe_max_tiles(pairs: int, num_experts: int, tile: int) -> int:
+    """The most tiles `pairs` rows can fill when grouped by expert: every expert may end in one partial tile."""
+    return pairs // tile + min(num_experts, pairs)
+
+
+def moe_align(ids: torch.Tensor, num_experts: int, tile: int, sorted_rows: torch.Tensor, tile_expert: torch.Tensor) -> None:
+    """Groups the pairs (token, choice), numbered in the order of `ids`, by expert into tiles of `tile` rows:
+    sorted_rows[tiles * tile] (pair numbers, -1 = padding) and tile_expert[tiles] (-1 = no such tile)."""
+    _need_cuda(ids, sorted_rows, tile_expert)
+    _i32(ids, "ids")
+    _i32(sorted_rows, "sorted_rows")
+    _i32(tile_expert, "tile_expert")
+    tiles = tile_expert.numel()
+    if sorted_rows.numel() != tiles * tile or tiles < moe_max_tiles(ids.numel(), num_experts, tile):
+        raise KernelError("moe_align: the tile buffers do not fit")
+    lib = build.load_library("moe")
+    _call(lib, lib.tllm_moe_align, _ptr(ids), ids.numel(), num_experts, tile, tiles, _ptr(sorted_rows), _ptr(tile_expert), _stream())
+
+
+def moe_linear(a: torch.Tensor, w: torch.Tensor, sorted_rows: torch.Tensor, tile_expert: torch.Tensor, tile: int,
+               out: torch.Tensor, rows_per_input: int = 1, gelu: bool = False) -> None:
+    """out[p] = act(w[expert of p] . a[p // rows_per_input]) for every pair p named in sorted_rows; w [experts, N, K],
+    out [pairs, N] in a's dtype or float32; act is the exact GELU or nothing."""
+    _need_cuda(a, w, sorted_rows, tile_expert, out)
+    n, k = w.shape[1], w.shape[2]
+    if a.shape[1] != k or a.stride(1) != 1 or a.dtype != w.dtype or not w.is_contiguous() or out.shape[1] != n or \
+            not out.is_contiguous() or out.dtype not in (a.dtype, torch.float32):
+        raise KernelError("moe_linear: shapes or dtypes do not fit")
+    lib = build.load_library("moe")
+    _call(lib, lib.tllm_moe_linear, _ptr(a), a.stride(0), _ptr(w), _ptr(sorted_rows), _ptr(tile_expert), _ptr(out), n, k,
+          rows_per_input, tile, tile_expert.numel(), 1 if gelu else 0, _code(a.dtype), _code(out.dtype), _stream())
+
+
+def moe_combine(y: torch.Tensor, weights: torch.Tensor, shared: Optional[torch.Tensor], logits: Optional[torch.Tensor],
+                gate_col: int, resid: torch.Tensor) -> None:
+    """resid[t] += sum_c weights[t, c] * y[t * top + c] + sigmoid(logits[t, gate_col]) * shared[t] (the last term only
+    with `shared`); all float32."""
+    _need_cuda(y, weights, shared, logits, resid)
+    t, width = resid.shape
+    top = weights.shape[1]
+    if y.shape != (t * top, width) or any(x.dtype != torch.float32 or not x.is_contiguous() for x in (y, weights, resid)) or \
+            (shared is not None and (shared.shape != resid.shape or shared.dtype != torch.float32 or not shared.is_contiguous()
+                                     or logits is None or logits.dtype != torch.float32 or logits.shape[1] <= gate_col)):
+        raise KernelError("moe_combine: shapes or dtypes do not fit")
+    lib = build.load_library("moe")
+    _call(lib, lib.tllm_moe_combine, _ptr(y), _ptr(weights), top, _ptr(shared), _ptr(logits),
+          0 if logits is None else logits.stride(0), gate_col, _ptr(resid), t, width, _stream())
 
 
 # ----------------------------------------------------------------------------- matrix products
@@ -789,7 +1054,8 @@ def sample(logits: torch.Tensor, work: torch.Tensor, temperature: torch.Tensor, 
                                 _ptr(seeds), _ptr(counters), _ptr(out), _ptr(status), _stream())
 
 
-ALL_LIBRARIES = ("elementwise", "linear_generic", "linear_tc", "attention_generic", "recurrence", "sampling")
+ALL_LIBRARIES = ("elementwise", "linear_generic", "linear_tc", "attention_generic", "recurrence", "linear_attention",
+                 "window_attention", "moe", "sampling")
 
 
 ATTENTION_HEAD_DIMS = (16, 32, 48, 64, 128)   # head sizes `build_all` compiles ahead; others compile on first use

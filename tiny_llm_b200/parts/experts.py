@@ -1,0 +1,86 @@
+"""Mixture of experts: many small feed-forwards W_down act(W_up h), of which every token uses `top`.
+
+Router: z = W_router h in 32-bit, s = sigmoid(z).  The experts with the largest s + correction are chosen (the
+correction, one learned number per expert, steers the choice only); the chosen experts' outputs are summed with the
+weights s * route_scale, not renormalised.  A shared expert of the same form runs for every token and is added times
+sigmoid(w_sg . h), one number per token.  act is the exact (erf) GELU.
+
+The experts' matrices are stacked at load ([experts, ff, hidden] and [experts, hidden, ff]); a step sorts its
+(token, choice) pairs by expert into tiles of rows on the device, so that one grouped product serves all experts and
+nothing about the routing reaches the host.  The router's rows and the shared gate's row are one matrix."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import ops
+from ..weights import COMPUTE, FLOAT32, WeightSpec
+from .feed_forward import scaled_matrix
+from .registry import register_part
+
+
+class RoutedExperts:
+    graph_safe = True
+
+    def __init__(self, hidden_size: int, num_experts: int, top: int, expert_size: int, route_scale: float = 1.0,
+                 shared_size: Optional[int] = None, out_scale: float = 1.0):
+        if not 0 < top <= num_experts:
+            raise ValueError(f"{top} of {num_experts} experts cannot be chosen")
+        self.hidden_size, self.num_experts, self.top = hidden_size, num_experts, top
+        self.expert_size, self.shared_size = expert_size, shared_size
+        self.route_scale = float(route_scale)
+        self.out_scale = float(out_scale)
+        self.w_route = self.correction = self.w_up = self.w_down = self.w_shared_up = self.w_shared_down = None
+
+    def weight_specs(self, prefix: str):
+        h, f = self.hidden_size, self.expert_size
+        specs = [WeightSpec(prefix + "router", (self.num_experts, h), COMPUTE),
+                 WeightSpec(prefix + "correction", (self.num_experts,), FLOAT32, init=("normal", 0.3))]
+        for e in range(self.num_experts):
+            specs += [WeightSpec(prefix + f"e{e}.up", (f, h), COMPUTE), WeightSpec(prefix + f"e{e}.down", (h, f), COMPUTE)]
+        if self.shared_size is not None:
+            specs += [WeightSpec(prefix + "shared.up", (self.shared_size, h), COMPUTE),
+                      WeightSpec(prefix + "shared.down", (h, self.shared_size), COMPUTE),
+                      WeightSpec(prefix + "shared.sg", (1, h), COMPUTE)]
+        return specs
+
+    def load(self, prefix: str, weights) -> None:
+        n = self.num_experts
+        rows = [weights[prefix + "router"]] + ([weights[prefix + "shared.sg"]] if self.shared_size is not None else [])
+        self.w_route = torch.cat(rows, dim=0).contiguous()
+        self.correction = weights[prefix + "correction"]
+        self.w_up = torch.stack([weights[prefix + f"e{e}.up"] for e in range(n)]).contiguous()
+        self.w_down = torch.stack([scaled_matrix(weights[prefix + f"e{e}.down"], self.out_scale) for e in range(n)]).contiguous()
+        if self.shared_size is not None:
+            self.w_shared_up = weights[prefix + "shared.up"]
+            self.w_shared_down = scaled_matrix(weights[prefix + "shared.down"], self.out_scale)
+
+    def forward(self, ctx, h, resid) -> None:
+        t = h.shape[0]
+        n, top, ws = self.num_experts, self.top, ctx.workspace
+        logits = ws.get("moe_logits", (t, self.w_route.shape[0]), torch.float32)
+        ops.linear(h, self.w_route, logits)
+        ids = ws.get("moe_ids", (t, top), torch.int32)
+        weights = ws.get("moe_weights", (t, top), torch.float32)
+        ops.moe_route(logits, n, self.correction, self.route_scale, ids, weights)
+        tile = ops.moe_tile_rows(t * top, n)
+        tiles = ops.moe_max_tiles(t * top, n, tile)
+        sorted_rows = ws.get("moe_rows", (tiles * tile,), torch.int32)
+        tile_expert = ws.get("moe_tile_expert", (tiles,), torch.int32)
+        ops.moe_align(ids, n, tile, sorted_rows, tile_expert)
+        act = ws.get("moe_act", (t * top, self.expert_size), ctx.dtype)
+        ops.moe_linear(h, self.w_up, sorted_rows, tile_expert, tile, act, rows_per_input=top, gelu=True)
+        y = ws.get("moe_y", (t * top, self.hidden_size), torch.float32)
+        ops.moe_linear(act, self.w_down, sorted_rows, tile_expert, tile, y, rows_per_input=1, gelu=False)
+        shared = None
+        if self.shared_size is not None:
+            sact = ws.get("ffn_act", (t, self.shared_size), ctx.dtype)
+            ops.linear(h, self.w_shared_up, sact)
+            ops.gelu(sact, sact)
+            shared = ws.get("moe_shared", (t, self.hidden_size), torch.float32)
+            ops.linear(sact, self.w_shared_down, shared)
+        ops.moe_combine(y, weights, shared, logits, n, resid)
+
+
+register_part("ffn", "routed_experts", RoutedExperts)

@@ -10,16 +10,18 @@ from .registry import register_part
 class RMSNorm:
     graph_safe = True   # launches kernels only: a step through this part can be captured in a CUDA graph
 
-    def __init__(self, size: int, eps: float):
+    def __init__(self, size: int, eps: float, weight_suffix: str = ".weight"):
+        """`weight_suffix`: what the weight is called behind the part's name ("" when the name is the tensor's)."""
         self.size = size
         self.eps = float(eps)
+        self.weight_suffix = weight_suffix
         self.weight = None
 
     def weight_specs(self, prefix: str):
-        return [WeightSpec(prefix + ".weight", (self.size,), FLOAT32)]
+        return [WeightSpec(prefix + self.weight_suffix, (self.size,), FLOAT32)]
 
     def load(self, prefix: str, weights) -> None:
-        self.weight = weights[prefix + ".weight"]
+        self.weight = weights[prefix + self.weight_suffix]
 
     def forward(self, ctx, x, rows=None):
         n = x.shape[0] if rows is None else rows.shape[0]

@@ -1,5 +1,10 @@
 """Recurrent mixers: a state of fixed size per request instead of keys and values.
 
+Linear attention (below minGRU): a matrix state per head, S_t = diag(a_t) S_(t-1) + k_t v_t^T, o_t = S_t^T q_t, with no
+softmax and no denominator.  `Retention` fixes one decay per head; `GatedLinearAttention` computes a decay per key
+channel and token from a low-rank projection of the input.  Both normalise every head's output, multiply it by
+silu(Wg h) and project it; the state [heads, key size, value size] is 32-bit in the request's state slot.
+
 minGRU.  A gated recurrence whose gates read the current token only, so all gates of a portion come from one
 matrix product and only the element-wise recurrence walks the tokens:
     z_t = sigmoid(Wz h_t + bz)                      how much of the candidate enters
@@ -55,3 +60,139 @@ class MinGRU:
 
 
 register_part("mixer", "min_gru", MinGRU)
+
+
+class LinearAttention:
+    """S_t = diag(a_t) S_(t-1) + (ks k_t) v_t^T;  o_t = S_t^T (qs q_t);  y_t = Wo (norm(o_t) * silu(Wg h_t)), head by head.
+
+    The decay a_t is what the subclasses differ in.  The input matrices are fused into one product at load
+    ([q | k | v | g | more] rows); the decays, the recurrence, the state and the norm are 32-bit, the projections are
+    the engine's dtype.  `norm_weight`: the per-head norm multiplies by a learned vector of the value size (shared by
+    the heads) stored as `<prefix>norm`; without it the head's output is only divided by its root mean square."""
+    graph_safe = True
+
+    def __init__(self, hidden_size: int, num_heads: int, key_dim: int, value_dim: int, eps: float,
+                 q_scale: float = 1.0, k_scale: float = 1.0, norm_weight: bool = False, out_scale: float = 1.0,
+                 shares_cache: bool = False):
+        if shares_cache:
+            raise ValueError("a recurrent mixer's state cannot be read by another layer call")
+        self.hidden_size, self.num_heads, self.key_dim, self.value_dim = hidden_size, num_heads, key_dim, value_dim
+        self.eps, self.q_scale, self.k_scale = float(eps), float(q_scale), float(k_scale)
+        self.norm_weight = norm_weight
+        self.out_scale = float(out_scale)
+        self.qk = num_heads * key_dim
+        self.vg = num_heads * value_dim
+        self.w_in = self.w_o = self.w_norm = None
+
+    def cache_need(self):
+        return StateNeed((self.num_heads, self.key_dim, self.value_dim), torch.float32)
+
+    # what a subclass adds
+    def extra_rows(self) -> int:
+        """Rows the subclass appends to the fused input matrix (behind q, k, v, g)."""
+        return 0
+
+    def extra_weight_specs(self, prefix: str):
+        return []
+
+    def extra_load(self, prefix: str, weights):
+        return []
+
+    def decay_args(self, ctx, proj) -> dict:
+        raise NotImplementedError
+
+    def weight_specs(self, prefix: str):
+        h = self.hidden_size
+        specs = [WeightSpec(prefix + "q", (self.qk, h), COMPUTE), WeightSpec(prefix + "k", (self.qk, h), COMPUTE),
+                 WeightSpec(prefix + "v", (self.vg, h), COMPUTE), WeightSpec(prefix + "g", (self.vg, h), COMPUTE),
+                 WeightSpec(prefix + "o", (h, self.vg), COMPUTE)]
+        if self.norm_weight:
+            specs.append(WeightSpec(prefix + "norm", (self.value_dim,), FLOAT32))
+        return specs + self.extra_weight_specs(prefix)
+
+    def load(self, prefix: str, weights) -> None:
+        rows = [weights[prefix + n] for n in ("q", "k", "v", "g")] + self.extra_load(prefix, weights)
+        self.w_in = torch.cat(rows, dim=0).contiguous()
+        self.w_o = scaled_matrix(weights[prefix + "o"], self.out_scale)
+        self.w_norm = weights[prefix + "norm"] if self.norm_weight else None
+
+    def forward(self, ctx, h, resid, cache) -> None:
+        t = h.shape[0]
+        qk, vg = self.qk, self.vg
+        width = 2 * qk + 2 * vg + self.extra_rows()
+        # the row stride is a multiple of 8 values so that a slice of the rows can feed a tensor-core product
+        proj = ctx.workspace.get("lin_attn_in", (t, -(-width // 8) * 8), ctx.dtype)[:, :width]
+        ops.linear(h, self.w_in, proj, cluster_slices=True)
+        o = ctx.workspace.get("lin_attn_o", (t, vg), torch.float32)
+        ops.linear_attention_scan(proj[:, :qk], proj[:, qk:2 * qk], proj[:, 2 * qk:2 * qk + vg], self.num_heads,
+                                  self.key_dim, self.value_dim, cache.state, ctx.batch, o, self.q_scale, self.k_scale,
+                                  workspace=ctx.workspace, **self.decay_args(ctx, proj))
+        y = ctx.workspace.get("lin_attn_y", (t, vg), ctx.dtype)
+        ops.head_norm_gate(o, self.w_norm, proj[:, 2 * qk + vg:2 * qk + 2 * vg], self.num_heads, self.value_dim,
+                           self.eps, y)
+        ops.linear(y, self.w_o, resid, accumulate=True)
+
+
+class Retention(LinearAttention):
+    """Linear attention with one fixed decay per head (a_t = decay_h for every key channel and token); keys are
+    scaled by key_dim^(-1/2); every head's output is divided by its root mean square, without a weight."""
+
+    def __init__(self, hidden_size: int, num_heads: int, key_dim: int, value_dim: int, decay, eps: float, **kw):
+        if len(decay) != num_heads:
+            raise ValueError(f"{len(decay)} decays for {num_heads} heads")
+        super().__init__(hidden_size, num_heads, key_dim, value_dim, eps, k_scale=key_dim ** -0.5, **kw)
+        self.decay = tuple(float(d) for d in decay)
+        self.decay_dev = None
+
+    def extra_load(self, prefix, weights):
+        self.decay_dev = torch.tensor(self.decay, dtype=torch.float32, device=weights[prefix + "o"].device)
+        return []
+
+    def decay_args(self, ctx, proj):
+        return {"head_decay": self.decay_dev}
+
+
+class GatedLinearAttention(LinearAttention):
+    """Linear attention with a decay per key channel and token: a_t = sigmoid(Wa2 (Wa1 h_t) + b)^(1/tau), a low-rank
+    projection (rank = rows of Wa1).  Queries are scaled by key_dim^(-1/2); every head's output is RMS-normed with a
+    weight of the value size.  Wa1 rides in the fused input product; the second product leaves 32-bit rows, and the
+    bias, the sigmoid and the power are taken in 32-bit inside the recurrence kernel."""
+
+    def __init__(self, hidden_size: int, num_heads: int, key_dim: int, value_dim: int, tau: float, eps: float,
+                 rank: int = 0, **kw):
+        super().__init__(hidden_size, num_heads, key_dim, value_dim, eps, q_scale=key_dim ** -0.5, norm_weight=True, **kw)
+        self.tau = float(tau)
+        self.rank = rank          # 0: read from the stored tensor's shape
+        self.w_a2 = self.b_a2 = None
+
+    def extra_weight_specs(self, prefix):
+        r = self.rank if self.rank else None    # None: any number of rows
+        return [WeightSpec(prefix + "a1", (r, self.hidden_size), COMPUTE), WeightSpec(prefix + "a2", (self.qk, r), COMPUTE),
+                WeightSpec(prefix + "a2.b", (self.qk,), FLOAT32, init=("normal", 1.0))]
+
+    def extra_load(self, prefix, weights):
+        a1 = weights[prefix + "a1"]
+        self.rank = a1.shape[0]
+        a2 = weights[prefix + "a2"]
+        if a2.shape[1] != self.rank:
+            raise ValueError(f"{prefix}a2 has {a2.shape[1]} columns, {prefix}a1 {self.rank} rows")
+        pad = -(-self.rank // 8) * 8     # K of the second product as a multiple of 8 (zero columns add nothing)
+        self.w_a2 = torch.zeros(self.qk, pad, dtype=a2.dtype, device=a2.device)
+        self.w_a2[:, :self.rank] = a2
+        self.b_a2 = weights[prefix + "a2.b"]
+        self._pad = pad - self.rank
+        return [a1] + ([torch.zeros(self._pad, self.hidden_size, dtype=a1.dtype, device=a1.device)] if self._pad else [])
+
+    def extra_rows(self):
+        return self.w_a2.shape[1] if self.w_a2 is not None else self.rank
+
+    def decay_args(self, ctx, proj):
+        t = proj.shape[0]
+        off = 2 * self.qk + 2 * self.vg
+        z = ctx.workspace.get("lin_attn_gate", (t, self.qk), torch.float32)
+        ops.linear(proj[:, off:off + self.w_a2.shape[1]], self.w_a2, z)
+        return {"gate": z, "gate_bias": self.b_a2, "inv_tau": 1.0 / self.tau}
+
+
+register_part("mixer", "retention", Retention)
+register_part("mixer", "gated_linear_attention", GatedLinearAttention)

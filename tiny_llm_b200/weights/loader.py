@@ -31,6 +31,9 @@ class WeightSpec:
     shape: Tuple[int, ...]
     keep: str = COMPUTE
     alias_of: Optional[str] = None
+    # A size given as None is read from the stored tensor (a rank that no configuration key names); random-weights
+    # mode makes it `free_dim`.
+    free_dim: int = 16
     # how random-weights mode fills the tensor when the default (matrices N(0, initializer_range), float32 vectors 1)
     # does not suit it: ("normal", std), ("const", value) or ("uniform", low, high)
     init: Optional[Tuple] = None
@@ -142,7 +145,8 @@ def check_against(specs: Mapping[str, WeightSpec], src, ignore: Sequence[str] = 
     for n, s in specs.items():
         if n not in src:
             continue
-        if tuple(src.shape(n)) != tuple(s.shape):
+        found = tuple(src.shape(n))
+        if len(found) != len(s.shape) or any(want is not None and want != got for want, got in zip(s.shape, found)):
             wrong.append(f"{n}: expected shape {list(s.shape)}, found {list(src.shape(n))}")
         elif s.keep == INT32 and src.dtype(n).is_floating_point:
             wrong.append(f"{n}: expected an integer table, found {src.dtype(n)}")

@@ -5,6 +5,7 @@ depend on which other tensors the model has.  The reference has no such mode; it
 weights with ramps (tests/runtime/cuda/test_attention_runtime.cpp:165-174)."""
 from __future__ import annotations
 
+import dataclasses
 import hashlib
 import json
 import os
@@ -31,6 +32,8 @@ def random_state(specs: Mapping[str, WeightSpec], seed: int, std: float, dtype: 
     out = {}
     device = torch.device(device)
     for name, s in specs.items():
+        if any(d is None for d in s.shape):   # a size that only the stored tensor fixes
+            s = dataclasses.replace(s, shape=tuple(s.free_dim if d is None else d for d in s.shape))
         if s.keep == INT32:
             out[name] = torch.zeros(s.shape, dtype=torch.int32, device=device)
         elif s.init is not None and s.init[0] == "const":
