@@ -14,7 +14,8 @@ config.json keys (every size and every constant that differs between models of t
     retention mixer  {"heads", "dim", "vdim", "decay": [one number per head]}
     parallel mixer   {"left": {"heads", "kv_heads", "dim", "vdim", "scale", "softcap" | absent,
                                "mask": {"size", "pool" | absent} | absent, "rot": {"dims", "base"} | absent},
-                      "right": {"heads", "dim", "vdim", "tau"}}
+                      "right": {"heads", "dim", "vdim", "tau", "rank" | absent}}   (the rank of the decay's projection
+                               is the stored tensors' when it is absent; random-weights mode then takes 16)
     mlp              {"kind": "moe", "expert": {"ff"}, "router": {"experts", "top", "scale"}, "shared": {"ff"} | absent}
 
 Tensor names: `embed`, `pos`, `head`, `final.norm`, and per layer `l<i>.norm1`, `l<i>.norm2`, `l<i>.mix.*`
@@ -70,6 +71,8 @@ def _check_right(m: dict, where: str) -> None:
         _pos_int(m, k, where)
     if _number(m, "tau", where) <= 0:
         raise ConfigError(f'config.json: {where}: "tau" must be positive')
+    if m.get("rank") is not None:
+        _pos_int(m, "rank", where)
 
 
 def _check_mlp(mlp: dict, where: str) -> None:
@@ -147,7 +150,7 @@ class ZozenexConfig:
             "rot_base": float(rot.get("base", 10000.0)), "rotate_values": bool(rot)})
         right = PartSpec("gated_linear_attention", {
             "hidden_size": w, "num_heads": ri["heads"], "key_dim": ri["dim"], "value_dim": ri["vdim"],
-            "tau": float(ri["tau"]), "eps": eps})
+            "tau": float(ri["tau"]), "eps": eps, "rank": ri.get("rank") or 0})
         return PartSpec("side_by_side", {"hidden_size": w, "eps": eps, "weight": 0.5,
                                          "branches": (("left.", left, "left.out"), ("right.", right, "right.out"))})
 
