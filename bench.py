@@ -14,7 +14,9 @@ roofline of every decode point, and the clocks seen while timing.
 
 `--design dunelix` measures another registered design instead (its own line, no record): prefill and decode of a
 Dunelix model at the TinyLlama layer sizes beside the Llama decoder at equal sizes, and its kernels alone beside their
-like kernels, each against its roofline (`--only decode` with it: the decode points alone)."""
+like kernels, each against its roofline (`--only decode` with it: the decode points alone).  `--design zozenex` does
+the same for a Zozenex model (retention and gated linear attention, window attention with pooled blocks, routed
+experts) beside the Dunelix model at equal width, layers and vocabulary."""
 import argparse
 import json
 import os
@@ -538,6 +540,166 @@ def design_kernels(dtype, device, pk, tokens=2048):
     return out
 
 
+# `--design zozenex`: a Zozenex model (retention layers, every fourth layer window attention with pooled blocks beside
+# gated linear attention, routed experts with a shared one) at the same width, layers and vocabulary, beside the Dunelix
+# model above (the closest design the engine has: recurrent layers with an attention layer every fourth).
+def zozenex_shape(layers=DESIGN_LAYERS, width=2048, vocab=32000, window=1024, pool=64):
+    mlp = {"kind": "moe", "expert": {"ff": 1408}, "router": {"experts": 32, "top": 4, "scale": 2.0}, "shared": {"ff": 1408}}
+    ret = {"type": "retention", "mixer": {"heads": 16, "dim": 64, "vdim": 128,
+                                          "decay": [1.0 - 2.0 ** -(5.0 + 0.25 * i) for i in range(16)]}, "mlp": mlp}
+    par = {"type": "parallel", "mlp": mlp, "mixer": {
+        "left": {"heads": 16, "kv_heads": 4, "dim": 64, "vdim": 128, "scale": 0.125, "softcap": 30.0,
+                 "mask": {"size": window, "pool": pool}, "rot": {"dims": 64, "base": 10000.0}},
+        "right": {"heads": 8, "dim": 64, "vdim": 128, "tau": 16.0, "rank": 16}}}
+    return {"architecture": "Zozenex", "vocab": vocab, "width": width, "max_positions": CONTEXT, "norm": {"eps": 1e-6},
+            "initializer_range": 0.02, "layers": [par if i % 4 == 3 else ret for i in range(layers)]}
+
+
+def zozenex_decode_bytes(model, runner, batch, mean_ctx, itemsize):
+    """What a decode step must move: the weights once (of the experts only those that the batch's tokens are expected
+    to choose: E (1 - (1 - top / E)^batch) of E), the keys and values a request can see (its window and the block
+    rows before it), and the recurrent states read and written."""
+    total = 0
+    for blk in model.blocks:
+        f = blk.ffn
+        expert = 0 if f is None else 2 * f.expert_size * f.hidden_size * itemsize
+        chosen = 0.0 if f is None else f.num_experts * (1.0 - (1.0 - f.top / f.num_experts) ** batch)
+        total += 0 if f is None else (chosen - f.num_experts) * expert     # spec_weight_bytes counts every expert
+    total += spec_weight_bytes(model, itemsize)
+    for g in runner.cache.groups:
+        n = g.need
+        if n.stride > 1:
+            window = min(x.need.window for x in runner.cache.groups if x.need.window is not None)
+            seen = max(0, mean_ctx - window)
+        else:
+            seen = mean_ctx if n.window is None else min(mean_ctx, n.window)
+        total += batch * seen * g.bytes_per_token(itemsize)
+    for n in runner.cache.slots.needs:
+        numel = 1
+        for d in n.shape:
+            numel *= d
+        total += 2 * batch * 4 * numel
+    return int(total)
+
+
+def zozenex_kernels(dtype, device, pk, tokens=2048):
+    """The design's kernels alone at the sizes of one layer of the --design shape and `tokens` tokens of one prompt, and
+    their like kernels of the Dunelix and Llama paths: microseconds, achieved GB/s or TFLOP/s, share of the peak."""
+    import types
+    import torch
+    from tiny_llm_b200 import ops
+    from tiny_llm_b200.engine import Workspace
+    t, width, heads, kvh, kd, vd, window, pool, page = tokens, 2048, 16, 4, 64, 128, 1024, 64, PAGE
+    experts, top, ff = 32, 4, 1408
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=device)
+    out = {}
+    isz = 2 if dtype == torch.bfloat16 else 4
+
+    def mem(name, us, nbytes):
+        out[name] = {"us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1), "frac": round(nbytes / us / 1e3 / pk["hbm_gbs"], 3)}
+
+    def flop(name, us, flops):
+        out[name] = {"us": round(us, 2), "tflops": round(flops / us / 1e6, 1), "frac": round(flops / us / 1e6 / pk["bf16_tflops"], 3)}
+
+    ws = Workspace(torch.device(device))
+    batch = types.SimpleNamespace(cu_q=i32([0, t]), slots=i32([1]), num_requests=1, max_q_len=t)
+    # the recurrences: read q, k, v (and the gate's 32-bit rows), write 32-bit outputs
+    for name, h, gated in (("linear_attention_scan (retention, 16 heads)", 16, False), ("linear_attention_scan (gated, 8 heads)", 8, True)):
+        q, k = torch.randn(t, h * kd, device=device).to(dtype), torch.randn(t, h * kd, device=device).to(dtype)
+        v = torch.randn(t, h * vd, device=device).to(dtype)
+        state = torch.zeros(4, h, kd, vd, device=device)
+        o = torch.empty(t, h * vd, device=device)
+        kw = {"gate": torch.randn(t, h * kd, device=device), "gate_bias": torch.zeros(h * kd, device=device), "inv_tau": 1 / 16} \
+            if gated else {"head_decay": torch.full((h,), 0.97, device=device)}
+        mem(name, time_kernel(lambda: ops.linear_attention_scan(q, k, v, h, kd, vd, state, batch, o, 1.0, 0.125, workspace=ws, **kw), flush),
+            t * h * ((2 * kd + vd) * isz + vd * 4 + (kd * 4 if gated else 0)))
+        g = torch.randn(t, h * vd, device=device).to(dtype)
+        y = torch.empty(t, h * vd, dtype=dtype, device=device)
+        wn = torch.ones(vd, device=device)
+        if not gated:
+            mem("head_norm_gate", time_kernel(lambda: ops.head_norm_gate(o, wn, g, h, vd, 1e-6, y), flush), t * h * vd * (4 + 2 * isz))
+    zug = torch.randn(t, 3 * width, device=device).to(dtype)
+    bias = torch.zeros(width, device=device)
+    st = torch.zeros(4, width, device=device)
+    yy = torch.empty(t, width, dtype=dtype, device=device)
+    mem("min_gru_scan (like)", time_kernel(lambda: ops.min_gru_scan(zug, bias, bias, st, batch, yy, ws), flush), t * width * 4 * isz)
+    x = torch.randn(t, width, device=device)
+    resid = torch.zeros(t, width, device=device)
+    w1 = torch.ones(width, device=device)
+    mem("rms_norm_add", time_kernel(lambda: ops.rms_norm_add(x, w1, 1e-6, 0.5, resid), flush), t * width * 16)
+    mem("rms_norm (like)", time_kernel(lambda: ops.rms_norm(x, w1, 1e-6, yy), flush), t * width * (4 + isz))
+
+    # one request of `t` tokens from position 0 in pages of its own
+    pages = -(-t // page)
+    table = i32([list(range(pages))])
+    slots, pos = i32(list(range(t))), i32(list(range(t)))
+    meta = types.SimpleNamespace(token_request=i32([0] * t), positions=pos, cu_q=i32([0, t]), q_start=i32([0]),
+                                 num_requests=1, num_tokens=t, max_q_len=t, max_kv_len=t, num_leading_decodes=0)
+    qkv = torch.randn(t, (heads + kvh) * kd + kvh * vd, device=device).to(dtype)
+    kc = torch.zeros(pages, kvh, page, kd, dtype=dtype, device=device)
+    vc = torch.zeros(pages, kvh, page, vd, dtype=dtype, device=device)
+    pkc, pvc = torch.zeros_like(kc), torch.zeros_like(vc)
+    fk = torch.pow(torch.tensor(10000.0), -torch.arange(kd // 2, dtype=torch.float32) * 2 / kd).to(device)
+    fv = torch.pow(torch.tensor(10000.0), -torch.arange(vd // 2, dtype=torch.float32) * 2 / vd).to(device)
+    mem("rope_halves_kv_write (values rotated)", time_kernel(lambda: ops.rope_halves_kv_write(
+        qkv, pos, fk, kd, fv, heads, kvh, kvh, kd, vd, kc, vc, slots), flush), t * isz * (heads * kd * 2 + (kvh * kd + kvh * vd) * 2))
+    pslots = i32([(p // pool) if (p + 1) % pool == 0 else -1 for p in range(t)])
+    mem("pool_kv_blocks", time_kernel(lambda: ops.pool_kv_blocks(kc, vc, table, pkc, pvc, pslots, meta, pool), flush),
+        t * kvh * (kd + vd) * isz * (1 + 1 / pool))
+    att = torch.empty(t, heads * vd, dtype=dtype, device=device)
+    hb = torch.zeros(heads, device=device)
+    pairs = sum(min(p + 1, window) + max(0, (p - window - pool + 1) // pool + 1 if p - window - pool + 1 >= 0 else 0) for p in range(t))
+    flop("window_pool_attention (window 1024, pool 64)", time_kernel(lambda: ops.window_pool_attention(
+        qkv, heads, kvh, kd, vd, kc, vc, table, pkc, pvc, table, meta, att, 0.125, 30.0, hb, window, pool, fv), flush, repeats=5),
+        2.0 * pairs * heads * (kd + vd))
+    # like: the Dunelix attention (two maps, chunk 1024) and its rotation kernel
+    maps = 2
+    dq = torch.randn(t, (heads + kvh) * maps * kd + kvh * vd, device=device).to(dtype)
+    dk = torch.zeros(pages, kvh * maps, page, kd, dtype=dtype, device=device)
+    mem("rope_pairs_kv_write (like)", time_kernel(lambda: ops.rope_pairs_kv_write(dq, pos, fk, kd, heads * maps, kvh * maps, kvh, kd, vd,
+                                                                                 dk, vc, slots), flush),
+        t * isz * ((heads * maps * kd) * 2 + (kvh * maps * kd + kvh * vd) * 2))
+    per_map = torch.empty(t, heads * maps * vd, dtype=torch.float32, device=device)
+    dpairs = sum(min(p % 1024, p) + 1 for p in range(t))
+    flop("attention, two maps, chunk 1024 (like)", time_kernel(lambda: ops.paged_attention_maps(
+        dq, heads, kvh, maps, kd, vd, dk, vc, table, meta, per_map, 0.125, None, 1024), flush), 2.0 * dpairs * heads * maps * (kd + vd))
+
+    # the experts: routing, grouping, the two grouped products, the combine; like: dense products of as many rows
+    h_in = torch.randn(t, width, device=device).to(dtype)
+    logits = torch.randn(t, experts + 1, device=device)
+    corr = torch.zeros(experts, device=device)
+    ids = torch.empty(t, top, dtype=torch.int32, device=device)
+    wts = torch.empty(t, top, device=device)
+    tile = ops.moe_tile_rows(t * top, experts)
+    tiles = ops.moe_max_tiles(t * top, experts, tile)
+    rows = torch.empty(tiles * tile, dtype=torch.int32, device=device)
+    texp = torch.empty(tiles, dtype=torch.int32, device=device)
+
+    def route():
+        ops.moe_route(logits, experts, corr, 2.0, ids, wts)
+        ops.moe_align(ids, experts, tile, rows, texp)
+    mem("moe_route + moe_align", time_kernel(route, flush), t * (experts * 4 + top * 16))
+    w_up = (torch.randn(experts, ff, width, device=device) * 0.02).to(dtype)
+    w_down = (torch.randn(experts, width, ff, device=device) * 0.02).to(dtype)
+    act = torch.empty(t * top, ff, dtype=dtype, device=device)
+    yexp = torch.empty(t * top, width, device=device)
+    flop("moe_linear up + gelu", time_kernel(lambda: ops.moe_linear(h_in, w_up, rows, texp, tile, act, rows_per_input=top, gelu=True), flush, repeats=5),
+         2.0 * t * top * ff * width)
+    flop("moe_linear down", time_kernel(lambda: ops.moe_linear(act, w_down, rows, texp, tile, yexp, rows_per_input=1), flush, repeats=5),
+         2.0 * t * top * ff * width)
+    dense_in = torch.randn(t * top, width, device=device).to(dtype)
+    flop("linear of as many rows (like)", time_kernel(lambda: ops.linear(dense_in, w_up[0], act), flush), 2.0 * t * top * ff * width)
+    shared = torch.randn(t, width, device=device)
+    mem("moe_combine", time_kernel(lambda: ops.moe_combine(yexp, wts, shared, logits, experts, resid), flush),
+        t * width * 4 * (top + 3))
+    sact = torch.randn(t, ff, device=device).to(dtype)
+    mem("gelu", time_kernel(lambda: ops.gelu(sact, sact), flush), t * ff * 2 * isz)
+    gu = torch.randn(t, 2 * ff, device=device).to(dtype)
+    mem("silu_mul (like)", time_kernel(lambda: ops.silu_mul(gu, sact, 128), flush), t * ff * 3 * isz)
+    return out
+
+
 def design_run(args, dtype, device, pk):
     import gc
     import torch
@@ -546,15 +708,23 @@ def design_run(args, dtype, device, pk):
     itemsize = 2 if dtype == torch.bfloat16 else 4
     steps, warmup = min(max(1, args.steps), 32), max(3, min(args.warmup, 8))
     out = torch.zeros(64, dtype=torch.int32, device=device)
-    result = {"design": "dunelix", "dtype": args.dtype, "layers": DESIGN_LAYERS, "peaks": pk["source"],
-              "sizes": "width 2048, feed-forward 5632, vocabulary 32000; minGRU width 2048; attention 16 heads x 2 maps of 64, "
-                       "4 key/value heads, values of 128, chunk 1024; every fourth layer attention; beside: Llama decoder, "
-                       "32 heads of 64, 4 key/value heads, equal width, feed-forward, layers and vocabulary",
+    sizes = {"dunelix": "width 2048, feed-forward 5632, vocabulary 32000; minGRU width 2048; attention 16 heads x 2 maps of 64, "
+                        "4 key/value heads, values of 128, chunk 1024; every fourth layer attention; beside: Llama decoder, "
+                        "32 heads of 64, 4 key/value heads, equal width, feed-forward, layers and vocabulary",
+             "zozenex": "width 2048, vocabulary 32000; retention 16 heads, keys of 64, values of 128; every fourth layer window "
+                        "attention (16 heads, 4 key/value heads, keys of 64, values of 128, window 1024, blocks of 64) beside gated "
+                        "linear attention (8 heads, keys of 64, values of 128, rank 16); 32 experts of 1408, 4 chosen, a shared "
+                        "expert of 1408; beside: the Dunelix model of --design dunelix at equal width, layers and vocabulary"}
+    result = {"design": args.design, "dtype": args.dtype, "layers": DESIGN_LAYERS, "peaks": pk["source"],
+              "sizes": sizes[args.design],
               "l2": "whole steps: weights larger than L2; kernels alone: L2 flushed before every timed call"}
     sampler = ClockSampler().start()
-    for label in ("dunelix", "llama")[:1 if args.only == "decode" else 2]:
+    labels = ("dunelix", "llama") if args.design == "dunelix" else ("zozenex", "dunelix")
+    for label in labels[:1 if args.only == "decode" else 2]:
         if label == "dunelix":
             cfg, model = build_design(dunelix_shape(), dtype, device)
+        elif label == "zozenex":
+            cfg, model = build_design(zozenex_shape(), dtype, device)
         else:
             cfg, model = build_model(DESIGN_LAYERS, dtype, device)
         runner = make_runner(model, dtype, device, max_tokens=64 * CONTEXT, page_size=PAGE, max_requests=64,
@@ -566,6 +736,7 @@ def design_run(args, dtype, device, pk):
         for bsz in (8, 64):
             ms, launched, ctx = timed_decode(runner, bsz, CONTEXT - (REPEATS * steps + warmup), steps, warmup, out, repeats=REPEATS)
             moved = design_decode_bytes(model, runner, bsz, ctx, itemsize) if label == "dunelix" else \
+                zozenex_decode_bytes(model, runner, bsz, ctx, itemsize) if label == "zozenex" else \
                 decode_bytes(model, runner, bsz, ctx, itemsize)
             rec[f"decode_b{bsz}"] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(bsz * 1e3 / ms, 1),
                                      "hbm_frac": round(moved / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4), "gpu_launches": launched}
@@ -575,7 +746,7 @@ def design_run(args, dtype, device, pk):
         torch.cuda.empty_cache()
     result["clocks"] = sampler.stop()
     if dtype == torch.bfloat16 and args.only == "all":
-        result["kernels"] = design_kernels(dtype, device, pk)
+        result["kernels"] = (design_kernels if args.design == "dunelix" else zozenex_kernels)(dtype, device, pk)
     ops.check_status()
     print(json.dumps(result))
     return 0
@@ -600,7 +771,7 @@ def main():
     ap.add_argument("--page-size", type=int, default=PAGE, help="tokens per page of the cache")
     ap.add_argument("--shape", default="tinyllama", choices=["tinyllama"] + list(OTHER_SHAPES),
                     help="layer sizes for --only runs (profiler captures of the other models' kernels)")
-    ap.add_argument("--design", default=None, choices=["dunelix"],
+    ap.add_argument("--design", default=None, choices=["dunelix", "zozenex"],
                     help="instead of the flagship run: this design's prefill and decode at real layer sizes beside the Llama "
                          "decoder at equal sizes, and its kernels beside their like kernels (one plain line, no record)")
     ap.add_argument("--quick", action="store_true",

@@ -6,8 +6,9 @@
 //   of `tile` rows: sorted_rows[tile * tile_rows + i] is a pair's number or -1 (padding), tile_expert[tile] the
 //   tile's expert or -1 (no such tile).  The host knows only the upper bound of the tile count.
 // moe_linear: out[row] = act(W[expert of the row's tile] . in[row / rows_per_input]) for every row named by
-//   sorted_rows.  W: [experts, N, K].  Every output element is one chain of fmaf over ascending k, so a row's
-//   result does not depend on the tile it landed in.
+//   sorted_rows.  W: [experts, N, K].  Two kernels: FFMA tiles for float32 (every output element is one chain of
+//   fmaf over ascending k, so a row's result does not depend on the tile it landed in) and mma.sync tiles for
+//   bfloat16 (below).
 // moe_combine: resid[t] += sum_c weight[t, c] * y[t * top + c] (+ sigmoid(gate logit) * shared[t]), choices in the
 //   order the router found them.
 // gelu: the exact (erf) GELU, element by element.
@@ -161,6 +162,119 @@ __global__ void __launch_bounds__(256) moe_linear_kernel(const T* __restrict__ i
   }
 }
 
+// ---- the grouped product on the tensor cores (bfloat16, mma.sync.m16n8k16, 32-bit sums)
+// A CTA owns BM rows of one expert's tile and 128 output columns; k in slices of 32 through a three-stage cp.async
+// ring (rows of 80 bytes in shared memory: ldmatrix reads eight of them without a bank conflict).  Eight warps:
+// 2 x 4 of 32 x 32 outputs for tiles of 64 rows, 1 x 8 of 16 x 16 for tiles of 16 rows (decode).  A rows are
+// gathered by the tile's row list; rows of padding read nothing.  K and the row strides are multiples of 8.
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void ldsm4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float* c, const unsigned* a, unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <typename TO, int BM, bool GELU>
+__global__ void __launch_bounds__(256) moe_linear_mma_kernel(const __nv_bfloat16* __restrict__ in, int ld_in,
+                                                             const __nv_bfloat16* __restrict__ w,
+                                                             const int* __restrict__ sorted_rows,
+                                                             const int* __restrict__ tile_expert, TO* __restrict__ out,
+                                                             int n, int k, int rows_per_input) {
+  constexpr int BN = 128, BK = 32, LDS = 40, STAGES = 3;
+  constexpr int WM = BM == 64 ? 2 : 1, WN = 8 / WM;           // warps along rows and columns
+  constexpr int WTM = BM / WM, WTN = BN / WN;                 // a warp's outputs: 32 x 32 or 16 x 16
+  constexpr int MI = WTM / 16, NI = WTN / 8;
+  __shared__ __align__(16) __nv_bfloat16 sa[STAGES][BM][LDS];
+  __shared__ __align__(16) __nv_bfloat16 sb[STAGES][BN][LDS];
+  __shared__ int srow[BM];
+  pdl_trigger();
+  pdl_wait();
+  const int e = tile_expert[blockIdx.x];
+  if (e < 0) return;
+  const int n0 = blockIdx.y * BN;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid < BM) srow[tid] = sorted_rows[(size_t)blockIdx.x * BM + tid];
+  __syncthreads();
+  const __nv_bfloat16* we = w + (size_t)e * n * k;
+  // what this thread copies per stage: one 16-byte piece of A (the first BM * 4 threads), two of B
+  const int a_row = tid >> 2, a_c = (tid & 3) * 8;
+  const bool a_mine = tid < BM * 4;
+  const int a_src = a_mine ? srow[a_row] : -1;
+  const __nv_bfloat16* a_ptr = in + (size_t)(a_src < 0 ? 0 : a_src / rows_per_input) * ld_in + a_c;
+  const int nk = (k + BK - 1) / BK;
+  auto load = [&](int stage, int kb) {
+    const int k0 = kb * BK;
+    if (a_mine) {
+      const bool ok = a_src >= 0 && k0 + a_c < k;
+      cp_async16(&sa[stage][a_row][a_c], a_ptr + (ok ? k0 : 0), ok);
+    }
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+      const int idx = tid + x * 256, r = idx >> 2, c = (idx & 3) * 8;
+      const bool ok = n0 + r < n && k0 + c < k;
+      cp_async16(&sb[stage][r][c], we + (size_t)(ok ? n0 + r : 0) * k + (ok ? k0 + c : 0), ok);
+    }
+  };
+  float acc[MI][NI][4];
+#pragma unroll
+  for (int i = 0; i < MI; ++i)
+#pragma unroll
+    for (int j = 0; j < NI; ++j)
+#pragma unroll
+      for (int x = 0; x < 4; ++x) acc[i][j][x] = 0.f;
+#pragma unroll
+  for (int s = 0; s < STAGES - 1; ++s) {
+    if (s < nk) load(s, s);
+    asm volatile("cp.async.commit_group;");
+  }
+  const int wm = warp / WN, wn = warp % WN;
+  for (int kb = 0; kb < nk; ++kb) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(STAGES - 2));
+    __syncthreads();
+    if (kb + STAGES - 1 < nk) load((kb + STAGES - 1) % STAGES, kb + STAGES - 1);
+    asm volatile("cp.async.commit_group;");
+    const int st = kb % STAGES;
+#pragma unroll
+    for (int kk = 0; kk < BK; kk += 16) {
+      unsigned af[MI][4], bf[NI][2];
+#pragma unroll
+      for (int i = 0; i < MI; ++i)
+        ldsm4(af[i][0], af[i][1], af[i][2], af[i][3], &sa[st][wm * WTM + i * 16 + (lane & 15)][kk + (lane >> 4) * 8]);
+#pragma unroll
+      for (int j = 0; j < NI; j += 2)
+        ldsm4(bf[j][0], bf[j][1], bf[j + 1][0], bf[j + 1][1],
+              &sb[st][wn * WTN + j * 8 + (lane & 7) + (lane >> 4) * 8][kk + ((lane >> 3) & 1) * 8]);
+#pragma unroll
+      for (int i = 0; i < MI; ++i)
+#pragma unroll
+        for (int j = 0; j < NI; ++j) mma_bf16(acc[i][j], af[i], bf[j][0], bf[j][1]);
+    }
+  }
+  asm volatile("cp.async.wait_group 0;");
+#pragma unroll
+  for (int i = 0; i < MI; ++i)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int row = srow[wm * WTM + i * 16 + (lane >> 2) + half * 8];
+      if (row < 0) continue;
+#pragma unroll
+      for (int j = 0; j < NI; ++j) {
+        const int c = n0 + wn * WTN + j * 8 + (lane & 3) * 2;
+        float v0 = acc[i][j][half * 2], v1 = acc[i][j][half * 2 + 1];
+        if (GELU) { v0 = gelu_erf(v0); v1 = gelu_erf(v1); }
+        if (c < n) out[(size_t)row * n + c] = from_f32<TO>(v0);
+        if (c + 1 < n) out[(size_t)row * n + c + 1] = from_f32<TO>(v1);
+      }
+    }
+}
+
 __global__ void moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ weights, int top,
                                    const float* __restrict__ shared, const float* __restrict__ logits, int ld_logits,
                                    int gate_col, float* __restrict__ resid, int width) {
@@ -221,13 +335,32 @@ static int moe_linear_launch(const void* in, int ld_in, const void* w, const int
   return TLLM_OK;
 }
 
-// in: [rows, k] rows of ld_in values; w: [experts, n, k]; out: [pairs, n] of out_dtype.
+// in: [rows, k] rows of ld_in values; w: [experts, n, k]; out: [pairs, n] of out_dtype.  use_mma != 0: bfloat16 products
+// whose K and row stride are multiples of 8 run on the tensor cores; everything else on the FFMA kernel.
 extern "C" int tllm_moe_linear(const void* in, int ld_in, const void* w, const int* sorted_rows, const int* tile_expert,
                                void* out, int n, int k, int rows_per_input, int tile, int max_tiles, int gelu, int dtype,
-                               int out_dtype, void* stream) {
+                               int out_dtype, int use_mma, void* stream) {
   TLLM_REQUIRE(n > 0 && k > 0 && rows_per_input > 0 && max_tiles > 0 && (tile == 16 || tile == 64), "moe_linear: sizes do not fit (tile %d)", tile);
   TLLM_REQUIRE(max_tiles <= 2147483647 && (n + 63) / 64 <= 65535, "moe_linear: the grid is too large");
   cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == TLLM_BF16 && use_mma && k % 8 == 0 && ld_in % 8 == 0 && ((uintptr_t)in & 15) == 0 && ((uintptr_t)w & 15) == 0) {
+    const dim3 grid((unsigned)max_tiles, (unsigned)((n + 127) / 128));
+    TLLM_REQUIRE((n + 127) / 128 <= 65535, "moe_linear: the grid is too large");
+#define TLLM_MOE_MMA(TO, BM, G)                                                                                           \
+  TLLM_LAUNCH("moe_linear", (moe_linear_mma_kernel<TO, BM, G>), grid, 256, 0, s, (const __nv_bfloat16*)in, ld_in,          \
+              (const __nv_bfloat16*)w, sorted_rows, tile_expert, (TO*)out, n, k, rows_per_input)
+    if (out_dtype == TLLM_BF16) {
+      if (tile == 16) { if (gelu) TLLM_MOE_MMA(__nv_bfloat16, 16, true); else TLLM_MOE_MMA(__nv_bfloat16, 16, false); }
+      else { if (gelu) TLLM_MOE_MMA(__nv_bfloat16, 64, true); else TLLM_MOE_MMA(__nv_bfloat16, 64, false); }
+      return TLLM_OK;
+    }
+    if (out_dtype == TLLM_F32) {
+      if (tile == 16) { if (gelu) TLLM_MOE_MMA(float, 16, true); else TLLM_MOE_MMA(float, 16, false); }
+      else { if (gelu) TLLM_MOE_MMA(float, 64, true); else TLLM_MOE_MMA(float, 64, false); }
+      return TLLM_OK;
+    }
+#undef TLLM_MOE_MMA
+  }
   if (dtype == TLLM_F32 && out_dtype == TLLM_F32)
     return moe_linear_launch<float, float>(in, ld_in, w, sorted_rows, tile_expert, out, n, k, rows_per_input, tile, max_tiles, gelu, s);
   if (dtype == TLLM_BF16 && out_dtype == TLLM_BF16)

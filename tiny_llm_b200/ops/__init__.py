@@ -97,7 +97,7 @@ def replay_tape(tape) -> None:
 def knobs():
     """The module's switches that decide which kernels a step launches; a tape or graph holds for one setting of them."""
     return (force_generic, split_k, cluster_mask, attention_tc, decode_wide_ctas, decode_cluster_merge, qkv_fused_rows,
-            linear_skinny, generic_attention_split, split_mixed_attention, min_gru_segment, linear_attention_segment, attention_maps_tc, attention_maps_decode_pairs, _pdl)
+            linear_skinny, generic_attention_split, split_mixed_attention, min_gru_segment, linear_attention_segment, moe_mma, attention_maps_tc, attention_maps_decode_pairs, _pdl)
 
 
 def _i32(t: Optional[torch.Tensor], name: str):
@@ -533,6 +533,10 @@ def moe_align(ids: torch.Tensor, num_experts: int, tile: int, sorted_rows: torch
     _call(lib, lib.tllm_moe_align, _ptr(ids), ids.numel(), num_experts, tile, tiles, _ptr(sorted_rows), _ptr(tile_expert), _stream())
 
 
+# bfloat16 grouped products on the tensor cores (0: the FFMA kernel, for comparisons)
+moe_mma = os.environ.get("TLLM_MOE_MMA", "1") != "0"
+
+
 def moe_linear(a: torch.Tensor, w: torch.Tensor, sorted_rows: torch.Tensor, tile_expert: torch.Tensor, tile: int,
                out: torch.Tensor, rows_per_input: int = 1, gelu: bool = False) -> None:
     """out[p] = act(w[expert of p] . a[p // rows_per_input]) for every pair p named in sorted_rows; w [experts, N, K],
@@ -544,7 +548,8 @@ def moe_linear(a: torch.Tensor, w: torch.Tensor, sorted_rows: torch.Tensor, tile
         raise KernelError("moe_linear: shapes or dtypes do not fit")
     lib = build.load_library("moe")
     _call(lib, lib.tllm_moe_linear, _ptr(a), a.stride(0), _ptr(w), _ptr(sorted_rows), _ptr(tile_expert), _ptr(out), n, k,
-          rows_per_input, tile, tile_expert.numel(), 1 if gelu else 0, _code(a.dtype), _code(out.dtype), _stream())
+          rows_per_input, tile, tile_expert.numel(), 1 if gelu else 0, _code(a.dtype), _code(out.dtype),
+          1 if (moe_mma and not force_generic) else 0, _stream())
 
 
 def moe_combine(y: torch.Tensor, weights: torch.Tensor, shared: Optional[torch.Tensor], logits: Optional[torch.Tensor],
