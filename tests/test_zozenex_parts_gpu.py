@@ -187,15 +187,19 @@ def paged_batch(lens_before, lens_new, page, stride=None):
     return tables, table.to(DEV), nxt + 1
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("dtype,tc", [(torch.float32, False), (torch.bfloat16, False), (torch.bfloat16, True)])
 @pytest.mark.parametrize("size,pool,page,cap,heads,kvh,kd,vd,rotv", [
-    (40, 8, 16, None, 4, 2, 16, 24, True), (9, 16, 4, 5.0, 2, 2, 24, 16, False), (33, 5, 8, 20.0, 3, 1, 32, 48, True),
+    (40, 8, 16, None, 8, 2, 16, 32, True), (9, 16, 4, 5.0, 2, 2, 24, 16, False), (33, 5, 8, 20.0, 3, 1, 32, 48, True),
     (7, 3, 4, None, 6, 3, 8, 8, False), (12, None, 16, None, 2, 1, 12, 10, True), (None, None, 8, 3.0, 1, 1, 16, 6, True),
     (64, 64, 16, None, 2, 1, 64, 64, False)])
-def test_window_and_block_attention_finds_the_planted_keys(dtype, size, pool, page, cap, heads, kvh, kd, vd, rotv):
+def test_window_and_block_attention_finds_the_planted_keys(dtype, tc, size, pool, page, cap, heads, kvh, kd, vd, rotv, monkeypatch):
     """Two requests of unequal length, first as one portion each (in one batch), then the last tokens of both one by
-    one: rotate-and-cache, block pooling and attention run as the mixer runs them, on poisoned caches."""
+    one: rotate-and-cache, block pooling and attention run as the mixer runs them, on poisoned caches.  `tc`: the
+    tensor-core kernel (for the sizes it takes; the others run on the CUDA-core kernel either way)."""
     from tiny_llm_b200 import ops
+    if tc and (kd % 16 or vd % 16):
+        pytest.skip("sizes the tensor-core kernel does not take")
+    monkeypatch.setattr(ops, "window_attention_tc", tc)
     from tiny_llm_b200.parts import half_frequencies
     lens, tail, scale, base = [413, 150], 20, 1.0, 1000.0
     pb = torch.linspace(-9.0, -7.0, heads)       # far below zero: a key that is not planted weighs about 1e-4
@@ -240,7 +244,11 @@ def test_window_and_block_attention_finds_the_planted_keys(dtype, size, pool, pa
                     b = p // pool
                     pslots.append(ptables[x][b // page] * page + b % page if (p + 1) % pool == 0 else -1)
         qkv = torch.stack(rows).to(dtype).to(DEV)
-        batch = SimpleNamespace(positions=i32(posl), token_request=i32(reql), num_tokens=len(posl))
+        cu = [0]
+        for n in new:
+            cu.append(cu[-1] + n)
+        batch = SimpleNamespace(positions=i32(posl), token_request=i32(reql), num_tokens=len(posl), cu_q=i32(cu),
+                                q_start=i32(before), num_requests=len(new), max_q_len=max(new))
         ops.rope_halves_kv_write(qkv, batch.positions, None, 0, fv, heads, kvh, kvh, kd, vd, kc, vc, i32(slots))
         if pool:
             ops.pool_kv_blocks(kc, vc, table, pkc, pvc, i32(pslots), batch, pool)

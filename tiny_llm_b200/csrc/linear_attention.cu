@@ -6,15 +6,15 @@
 // outputs of the engine's dtype.  The state of a request lives in state[slot, head, key, value] and is read at the
 // start of the request's tokens in the step and written back after the last one.
 //
-// scan: a CTA owns 32 value columns of one (request, head); a thread owns 16 state rows of one column in registers.
+// scan: a CTA owns 64 value columns of one (request, head); a thread owns 16 state rows of two columns in registers.
 // Eight tokens at a time are staged in shared memory (scaled queries and keys, decays); every thread walks them,
 // leaves its partial dot products, and the partials of a column are added over the row slices in a fixed order.
 // The operations on a state element are those of the sequence, whatever the cut into steps: the same bits.
 //
 // SEGMENTED (long portions): the tokens of a request are cut into segments; a first kernel walks every segment from
-// a zero state and keeps its end state and the product of its decays per row (S_end = diag(A) S_in + B); a second
-// finds each segment's S_in from the carried state and the summaries before it and walks the segment again, now
-// writing outputs.  The recurrence is linear in S, so the two ways differ by rounding only.
+// a zero state and keeps its end state and the product of its decays per row (S_end = diag(A) S_in + B); a small
+// kernel walks each request's summaries in order and leaves every segment's S_in in their place; a third walks the
+// segments again from there, now writing outputs.  The recurrence is linear in S, so the two ways differ by rounding only.
 //
 // head_norm_gate: y = o / sqrt(mean(o^2) + eps) * w * silu(g) per (token, head), 32-bit in, engine dtype out.
 #include "common.cuh"
@@ -24,7 +24,8 @@ TLLM_DEFINE_LAST_ERROR
 namespace tllm {
 
 constexpr int LA_ROWS = 16;   // state rows per thread
-constexpr int LA_COLS = 32;   // value columns per CTA
+constexpr int LA_CPT = 2;     // value columns per thread (lane and lane + 32)
+constexpr int LA_COLS = 32 * LA_CPT;   // value columns per CTA
 constexpr int LA_TOK = 8;     // tokens staged at once
 
 __device__ __forceinline__ float gate_decay(float x, float inv_tau) {
@@ -49,16 +50,16 @@ struct ScanArgs {
   // segments: 0 = serial
   int seg, max_segs;
   float* summary;            // [requests, max_segs, heads, (kd * vd) + kd]
-  float* carry;              // [requests, heads, kd, vd]
 };
 
 // mode 0: serial over the request's tokens, from and to `state`.
 // mode 1: a segment from a zero state; writes the end state and the decay products to `summary` (no outputs).
-// mode 2: a segment from the state composed of carry and the summaries before it; writes outputs, and the last
+// mode 2: a segment from the state that the prefix kernel left in `summary`; writes outputs, and the last
 //         segment of a request the state.
-template <typename T, int MODE>
+// GATED: a decay per key channel and token (staged with the queries and keys); else one per head.
+template <typename T, int MODE, bool GATED>
 __global__ void __launch_bounds__(512) linear_attention_scan_kernel(ScanArgs a) {
-  extern __shared__ float sm[];
+  extern __shared__ __align__(16) float sm[];
   pdl_trigger();
   const int lane = threadIdx.x, sl = threadIdx.y, nsl = blockDim.y;
   const int kdp = nsl * LA_ROWS;
@@ -69,10 +70,15 @@ __global__ void __launch_bounds__(512) linear_attention_scan_kernel(ScanArgs a) 
   const int h = blockIdx.y;
   const int r = MODE == 0 ? blockIdx.z : blockIdx.z / a.max_segs;
   const int sg = MODE == 0 ? 0 : blockIdx.z % a.max_segs;
-  const int col = blockIdx.x * LA_COLS + lane;
-  const bool col_ok = col < a.vd;
-  const int tid = sl * LA_COLS + lane, nthreads = nsl * LA_COLS;
-  const float hd = a.head_decay ? a.head_decay[h] : 1.f;
+  int col[LA_CPT];
+  bool col_ok[LA_CPT];
+#pragma unroll
+  for (int c = 0; c < LA_CPT; ++c) {
+    col[c] = blockIdx.x * LA_COLS + c * 32 + lane;
+    col_ok[c] = col[c] < a.vd;
+  }
+  const int tid = sl * 32 + lane, nthreads = nsl * 32;
+  const float hd = GATED ? 1.f : a.head_decay[h];
   pdl_wait();
   int t0 = a.cu_q[r], t1 = a.cu_q[r + 1];
   if (MODE != 0) {
@@ -86,27 +92,20 @@ __global__ void __launch_bounds__(512) linear_attention_scan_kernel(ScanArgs a) 
   const T* k = (const T*)a.k;
   const T* v = (const T*)a.v;
   float* st = a.state + (((size_t)a.slots[r] * a.heads + h) * a.kd) * a.vd;
-  float s[LA_ROWS];
+  const size_t per = (size_t)a.kd * a.vd + a.kd;
+  float* su = MODE == 0 ? nullptr : a.summary + (((size_t)r * a.max_segs + sg) * a.heads + h) * per;
+  float s[LA_CPT][LA_ROWS];
   float dprod[LA_ROWS];
 #pragma unroll
   for (int i = 0; i < LA_ROWS; ++i) {
     const int row = sl * LA_ROWS + i;
-    const bool ok = col_ok && row < a.kd;
     dprod[i] = 1.f;
-    if (MODE == 0) {
-      s[i] = ok ? st[(size_t)row * a.vd + col] : 0.f;
-    } else if (MODE == 1) {
-      s[i] = 0.f;
-    } else {
-      // the state at the segment's start: the carried state walked through the summaries before this segment
-      const float* cr = a.carry + (((size_t)r * a.heads + h) * a.kd) * a.vd;
-      float x = ok ? cr[(size_t)row * a.vd + col] : 0.f;
-      const size_t per = (size_t)a.kd * a.vd + a.kd;
-      for (int g = 0; g < sg; ++g) {
-        const float* su = a.summary + (((size_t)r * a.max_segs + g) * a.heads + h) * per;
-        if (ok) x = fmaf(su[(size_t)a.kd * a.vd + row], x, su[(size_t)row * a.vd + col]);
-      }
-      s[i] = x;
+#pragma unroll
+    for (int c = 0; c < LA_CPT; ++c) {
+      const bool ok = col_ok[c] && row < a.kd;
+      if (MODE == 0) s[c][i] = ok ? st[(size_t)row * a.vd + col[c]] : 0.f;
+      else if (MODE == 1) s[c][i] = 0.f;
+      else s[c][i] = ok ? su[(size_t)row * a.vd + col[c]] : 0.f;
     }
   }
   for (int tb = t0; tb < t1; tb += LA_TOK) {
@@ -118,31 +117,48 @@ __global__ void __launch_bounds__(512) linear_attention_scan_kernel(ScanArgs a) 
         const size_t t = (size_t)(tb + tt);
         qv = to_f32(q[t * a.ldq + h * a.kd + row]) * a.q_scale;
         kv = to_f32(k[t * a.ldk + h * a.kd + row]) * a.k_scale;
-        av = a.gate ? gate_decay(a.gate[t * a.ldg + h * a.kd + row] + a.gate_bias[h * a.kd + row], a.inv_tau) : hd;
+        if (GATED) av = gate_decay(a.gate[t * a.ldg + h * a.kd + row] + a.gate_bias[h * a.kd + row], a.inv_tau);
       }
       sq[idx] = qv;
       sk[idx] = kv;
-      sa[idx] = av;
+      if (GATED) sa[idx] = av;
     }
-    float vv[LA_TOK];
+    float vv[LA_CPT][LA_TOK];
 #pragma unroll
     for (int tt = 0; tt < LA_TOK; ++tt)
-      vv[tt] = (tt < nt && col_ok) ? to_f32(v[(size_t)(tb + tt) * a.ldv + h * a.vd + col]) : 0.f;
+#pragma unroll
+      for (int c = 0; c < LA_CPT; ++c)
+        vv[c][tt] = (tt < nt && col_ok[c]) ? to_f32(v[(size_t)(tb + tt) * a.ldv + h * a.vd + col[c]]) : 0.f;
     __syncthreads();
 #pragma unroll
     for (int tt = 0; tt < LA_TOK; ++tt) {
       if (tt < nt) {
-        const float* pq = sq + tt * kdp + sl * LA_ROWS;
-        const float* pk = sk + tt * kdp + sl * LA_ROWS;
-        const float* pa = sa + tt * kdp + sl * LA_ROWS;
-        float acc = 0.f;
+        const float4* pq = reinterpret_cast<const float4*>(sq + tt * kdp + sl * LA_ROWS);
+        const float4* pk = reinterpret_cast<const float4*>(sk + tt * kdp + sl * LA_ROWS);
+        const float4* pa = reinterpret_cast<const float4*>(sa + tt * kdp + sl * LA_ROWS);
+        float acc[LA_CPT];
 #pragma unroll
-        for (int i = 0; i < LA_ROWS; ++i) {
-          s[i] = fmaf(pa[i], s[i], pk[i] * vv[tt]);
-          if (MODE == 1) dprod[i] *= pa[i];
-          acc = fmaf(s[i], pq[i], acc);
+        for (int c = 0; c < LA_CPT; ++c) acc[c] = 0.f;
+#pragma unroll
+        for (int i4 = 0; i4 < LA_ROWS / 4; ++i4) {
+          const float4 q4 = pq[i4], k4 = pk[i4];
+          const float4 a4 = GATED ? pa[i4] : make_float4(hd, hd, hd, hd);
+          const float qa[4] = {q4.x, q4.y, q4.z, q4.w}, ka[4] = {k4.x, k4.y, k4.z, k4.w}, aa[4] = {a4.x, a4.y, a4.z, a4.w};
+#pragma unroll
+          for (int x = 0; x < 4; ++x) {
+            const int i = i4 * 4 + x;
+            if (MODE == 1) dprod[i] *= aa[x];
+#pragma unroll
+            for (int c = 0; c < LA_CPT; ++c) {
+              s[c][i] = fmaf(aa[x], s[c][i], ka[x] * vv[c][tt]);
+              acc[c] = fmaf(s[c][i], qa[x], acc[c]);
+            }
+          }
         }
-        if (MODE != 1) part[(tt * nsl + sl) * LA_COLS + lane] = acc;
+        if (MODE != 1) {
+#pragma unroll
+          for (int c = 0; c < LA_CPT; ++c) part[(tt * nsl + sl) * LA_COLS + c * 32 + lane] = acc[c];
+        }
       }
     }
     __syncthreads();
@@ -159,36 +175,49 @@ __global__ void __launch_bounds__(512) linear_attention_scan_kernel(ScanArgs a) 
     }
   }
   if (MODE == 1) {
-    const size_t per = (size_t)a.kd * a.vd + a.kd;
-    float* su = a.summary + (((size_t)r * a.max_segs + sg) * a.heads + h) * per;
 #pragma unroll
     for (int i = 0; i < LA_ROWS; ++i) {
       const int row = sl * LA_ROWS + i;
-      if (col_ok && row < a.kd) {
-        su[(size_t)row * a.vd + col] = s[i];
-        if (col == 0) su[(size_t)a.kd * a.vd + row] = dprod[i];
+      if (row < a.kd) {
+#pragma unroll
+        for (int c = 0; c < LA_CPT; ++c)
+          if (col_ok[c]) su[(size_t)row * a.vd + col[c]] = s[c][i];
+        if (col[0] == 0) su[(size_t)a.kd * a.vd + row] = dprod[i];
       }
     }
   } else if (MODE == 0 || last) {
 #pragma unroll
     for (int i = 0; i < LA_ROWS; ++i) {
       const int row = sl * LA_ROWS + i;
-      if (col_ok && row < a.kd) st[(size_t)row * a.vd + col] = s[i];
+#pragma unroll
+      for (int c = 0; c < LA_CPT; ++c)
+        if (col_ok[c] && row < a.kd) st[(size_t)row * a.vd + col[c]] = s[c][i];
     }
   }
 }
 
-// The state as earlier steps left it, set aside before the segments run: the last segment of a request overwrites the
-// state while other segments of the same request may not have read it yet.
-__global__ void linear_attention_carry_kernel(const float* __restrict__ state, const int* __restrict__ slots,
-                                              float* __restrict__ carry, long long per_request) {
+// Between the two passes over the segments: every state element walks its request's summaries in order and leaves,
+// in place of each segment's end state B_g, the state the segment starts from: x_0 = the carried state,
+// x_(g+1) = A_g x_g + B_g.  (The last segment's own summary was not written and is not read.)
+__global__ void linear_attention_prefix_kernel(ScanArgs a) {
   pdl_trigger();
   pdl_wait();
-  const int r = blockIdx.y;
-  const float* src = state + (size_t)slots[r] * per_request;
-  float* dst = carry + (size_t)r * per_request;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < per_request; i += (long long)gridDim.x * blockDim.x)
-    dst[i] = src[i];
+  const int h = blockIdx.y, r = blockIdx.z;
+  const int len = a.cu_q[r + 1] - a.cu_q[r];
+  const int nseg = (len + a.seg - 1) / a.seg;
+  const size_t per = (size_t)a.kd * a.vd + a.kd;
+  const float* st = a.state + (((size_t)a.slots[r] * a.heads + h) * a.kd) * a.vd;
+  for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < a.kd * a.vd; e += gridDim.x * blockDim.x) {
+    const int row = e / a.vd;
+    float x = st[e];
+    for (int g = 0; g < nseg; ++g) {
+      float* su = a.summary + (((size_t)r * a.max_segs + g) * a.heads + h) * per;
+      const bool more = g + 1 < nseg;
+      const float b = more ? su[e] : 0.f, d = more ? su[(size_t)a.kd * a.vd + row] : 0.f;
+      su[e] = x;
+      x = fmaf(d, x, b);
+    }
+  }
 }
 
 template <typename T>
@@ -224,8 +253,7 @@ using namespace tllm;
 // q, k: [T, heads * kd] rows of ldq / ldk values; v: [T, heads * vd] rows of ldv values (dtype: 0 float32, 1 bfloat16).
 // Exactly one of head_decay (float32 [heads]) and gate (float32 [T, heads * kd] rows of ldg values, with gate_bias
 // [heads * kd] and inv_tau) is given.  out: float32 [T, heads * vd].  seg > 0: segments of that many tokens with
-// `summary` (float32, n_requests * max_segs * heads * (kd * vd + kd) values, then n_requests * heads * kd * vd
-// values of carry); seg = 0: serial.
+// `summary` (float32, n_requests * max_segs * heads * (kd * vd + kd) values); seg = 0: serial.
 extern "C" int tllm_linear_attention_scan(const void* q, const void* k, const void* v, int ldq, int ldk, int ldv,
                                           const float* head_decay, const float* gate, int ldg, const float* gate_bias,
                                           float inv_tau, float q_scale, float k_scale, float* state, const int* slots,
@@ -242,38 +270,38 @@ extern "C" int tllm_linear_attention_scan(const void* q, const void* k, const vo
   a.head_decay = head_decay; a.gate = gate; a.ldg = ldg; a.gate_bias = gate_bias;
   a.inv_tau = inv_tau; a.q_scale = q_scale; a.k_scale = k_scale;
   a.state = state; a.slots = slots; a.cu_q = cu_q; a.out = out; a.heads = heads; a.kd = kd; a.vd = vd;
-  a.seg = 0; a.max_segs = 1; a.summary = nullptr; a.carry = nullptr;
+  a.seg = 0; a.max_segs = 1; a.summary = nullptr;
   const int nsl = (kd + LA_ROWS - 1) / LA_ROWS;
-  const dim3 block(LA_COLS, nsl);
+  const dim3 block(32, nsl);
   const size_t smem = (size_t)(3 * LA_TOK * nsl * LA_ROWS + LA_TOK * nsl * LA_COLS) * sizeof(float);
   const unsigned bx = (unsigned)((vd + LA_COLS - 1) / LA_COLS);
   cudaStream_t s = (cudaStream_t)stream;
+  const bool gated = gate != nullptr;
+#define TLLM_SCAN(name, T, MODE)                                                                          \
+  do {                                                                                                    \
+    if (gated) TLLM_LAUNCH(name, (linear_attention_scan_kernel<T, MODE, true>), grid, block, smem, s, a);  \
+    else TLLM_LAUNCH(name, (linear_attention_scan_kernel<T, MODE, false>), grid, block, smem, s, a);       \
+  } while (0)
   if (seg <= 0 || max_q_len <= seg) {
     TLLM_REQUIRE(n_requests <= 65535, "linear_attention_scan: %d requests exceed the grid", n_requests);
     const dim3 grid(bx, (unsigned)heads, (unsigned)n_requests);
-    if (dtype == TLLM_F32)
-      TLLM_LAUNCH("linear_attention_scan", (linear_attention_scan_kernel<float, 0>), grid, block, smem, s, a);
-    else
-      TLLM_LAUNCH("linear_attention_scan", (linear_attention_scan_kernel<__nv_bfloat16, 0>), grid, block, smem, s, a);
+    if (dtype == TLLM_F32) TLLM_SCAN("linear_attention_scan", float, 0);
+    else TLLM_SCAN("linear_attention_scan", __nv_bfloat16, 0);
     return TLLM_OK;
   }
   TLLM_REQUIRE(summary != nullptr, "linear_attention_scan: segments need a summary buffer");
   a.seg = seg;
   a.max_segs = (max_q_len + seg - 1) / seg;
   TLLM_REQUIRE((long long)a.max_segs * n_requests <= 65535, "linear_attention_scan: %d segments of %d requests exceed the grid", a.max_segs, n_requests);
-  const long long per_request = (long long)heads * kd * vd;
   a.summary = summary;
-  a.carry = summary + (size_t)n_requests * a.max_segs * heads * ((size_t)kd * vd + kd);
-  const dim3 cgrid((unsigned)((per_request + 1023) / 1024 > 64 ? 64 : (per_request + 1023) / 1024), (unsigned)n_requests);
-  TLLM_LAUNCH("linear_attention_carry", linear_attention_carry_kernel, cgrid, 256, 0, s, (const float*)state, slots, a.carry, per_request);
   const dim3 grid(bx, (unsigned)heads, (unsigned)(n_requests * a.max_segs));
-  if (dtype == TLLM_F32) {
-    TLLM_LAUNCH("linear_attention_summary", (linear_attention_scan_kernel<float, 1>), grid, block, smem, s, a);
-    TLLM_LAUNCH("linear_attention_segments", (linear_attention_scan_kernel<float, 2>), grid, block, smem, s, a);
-  } else {
-    TLLM_LAUNCH("linear_attention_summary", (linear_attention_scan_kernel<__nv_bfloat16, 1>), grid, block, smem, s, a);
-    TLLM_LAUNCH("linear_attention_segments", (linear_attention_scan_kernel<__nv_bfloat16, 2>), grid, block, smem, s, a);
-  }
+  const dim3 pgrid((unsigned)((kd * vd + 255) / 256), (unsigned)heads, (unsigned)n_requests);
+  if (dtype == TLLM_F32) TLLM_SCAN("linear_attention_summary", float, 1);
+  else TLLM_SCAN("linear_attention_summary", __nv_bfloat16, 1);
+  TLLM_LAUNCH("linear_attention_prefix", linear_attention_prefix_kernel, pgrid, 256, 0, s, a);
+  if (dtype == TLLM_F32) TLLM_SCAN("linear_attention_segments", float, 2);
+  else TLLM_SCAN("linear_attention_segments", __nv_bfloat16, 2);
+#undef TLLM_SCAN
   return TLLM_OK;
 }
 

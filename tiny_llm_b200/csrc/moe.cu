@@ -163,7 +163,7 @@ __global__ void __launch_bounds__(256) moe_linear_kernel(const T* __restrict__ i
 }
 
 // ---- the grouped product on the tensor cores (bfloat16, mma.sync.m16n8k16, 32-bit sums)
-// A CTA owns BM rows of one expert's tile and 128 output columns; k in slices of 32 through a three-stage cp.async
+// A CTA owns BM rows of one expert's tile and 128 output columns; k in slices of 32 through a three- or four-stage cp.async
 // ring (rows of 80 bytes in shared memory: ldmatrix reads eight of them without a bank conflict).  Eight warps:
 // 2 x 4 of 32 x 32 outputs for tiles of 64 rows, 1 x 8 of 16 x 16 for tiles of 16 rows (decode).  A rows are
 // gathered by the tile's row list; rows of padding read nothing.  K and the row strides are multiples of 8.
@@ -187,7 +187,7 @@ __global__ void __launch_bounds__(256) moe_linear_mma_kernel(const __nv_bfloat16
                                                              const int* __restrict__ sorted_rows,
                                                              const int* __restrict__ tile_expert, TO* __restrict__ out,
                                                              int n, int k, int rows_per_input) {
-  constexpr int BN = 128, BK = 32, LDS = 40, STAGES = 3;
+  constexpr int BN = 128, BK = 32, LDS = 40, STAGES = BM == 64 ? 3 : 4;
   constexpr int WM = BM == 64 ? 2 : 1, WN = 8 / WM;           // warps along rows and columns
   constexpr int WTM = BM / WM, WTN = BN / WN;                 // a warp's outputs: 32 x 32 or 16 x 16
   constexpr int MI = WTM / 16, NI = WTN / 8;

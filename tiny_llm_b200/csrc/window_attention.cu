@@ -14,6 +14,7 @@
 //   warp adds the 32 weighted value rows, lanes across the value's columns.  Blocks first, then tokens, by ascending
 //   position: the order of every sum depends on the position alone, not on the step's cut or the batch.
 #include "common.cuh"
+#include "window_attention.cuh"
 
 TLLM_DEFINE_LAST_ERROR
 
@@ -108,13 +109,21 @@ __global__ void pool_kv_blocks_kernel(const T* __restrict__ kcache, const T* __r
   for (int e = threadIdx.x; e < kd + vd; e += blockDim.x) {
     const bool is_k = e < kd;
     const int d = is_k ? e : e - kd;
+    const T* base = is_k ? kcache + h * k_head_stride + d : vcache + h * v_head_stride + d;
+    const long long page_stride = is_k ? k_page_stride : v_page_stride;
+    const int row = is_k ? kd : vd;
     float sum = 0.f;
-    for (int j = first; j <= p; ++j) {
-      const long long page = table[j / page_size];
-      const int off = j % page_size;
-      if (page < 0) continue;   // never: a token's page outlives its block's completion
-      sum += is_k ? to_f32(kcache[page * k_page_stride + h * k_head_stride + (long long)off * kd + d])
-                  : to_f32(vcache[page * v_page_stride + h * v_head_stride + (long long)off * vd + d]);
+    // eight loads in flight, added in the order of the positions
+    for (int j0 = first; j0 <= p; j0 += 8) {
+      float x[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int j = j0 + u;
+        const long long page = j <= p ? table[j / page_size] : -1;   // a token's page outlives its block's completion
+        x[u] = page >= 0 ? to_f32(base[page * page_stride + (long long)(j % page_size) * row]) : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) sum += x[u];
     }
     if (is_k) pk[ppage * pk_page_stride + h * pk_head_stride + poff * kd + d] = from_f32<T>(sum * inv);
     else pv[ppage * pv_page_stride + h * pv_head_stride + poff * vd + d] = from_f32<T>(sum * inv);
@@ -123,26 +132,6 @@ __global__ void pool_kv_blocks_kernel(const T* __restrict__ kcache, const T* __r
 
 constexpr int WA_WARPS = 4;
 constexpr int WA_MAX_VD = 512;
-
-struct WinArgs {
-  const void* qkv;      // queries at the front of every row
-  int row_stride;
-  int nh, nkv, kd, vd;
-  const void *k, *v;    // token pages
-  const int* table; int max_blocks;
-  long long k_page_stride, k_head_stride, v_page_stride, v_head_stride;
-  const void *pk, *pv;  // block pages (or null)
-  const int* ptable; int pmax_blocks;
-  long long pk_page_stride, pk_head_stride, pv_page_stride, pv_head_stride;
-  int page_size;
-  const int* positions; const int* token_request;
-  void* out;
-  float scale, cap;     // cap <= 0: none
-  const float* head_bias;
-  int window, pool;     // window <= 0: every key; pool <= 0: no blocks
-  const float* fv;      // frequencies of the value rotation, or null
-  int n_tokens;
-};
 
 template <typename T>
 __device__ __forceinline__ float dot_row(const float* __restrict__ q, const T* __restrict__ k, int kd) {

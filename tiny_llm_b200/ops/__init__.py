@@ -97,7 +97,7 @@ def replay_tape(tape) -> None:
 def knobs():
     """The module's switches that decide which kernels a step launches; a tape or graph holds for one setting of them."""
     return (force_generic, split_k, cluster_mask, attention_tc, decode_wide_ctas, decode_cluster_merge, qkv_fused_rows,
-            linear_skinny, generic_attention_split, split_mixed_attention, min_gru_segment, linear_attention_segment, moe_mma, attention_maps_tc, attention_maps_decode_pairs, _pdl)
+            linear_skinny, generic_attention_split, split_mixed_attention, min_gru_segment, linear_attention_segment, moe_mma, window_attention_tc, attention_maps_tc, attention_maps_decode_pairs, _pdl)
 
 
 def _i32(t: Optional[torch.Tensor], name: str):
@@ -348,8 +348,7 @@ def linear_attention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, hea
         seg = linear_attention_segment
         segs = -(-batch.max_q_len // seg)
         per = heads * (key_dim * value_dim + key_dim)
-        summary = workspace.get("lin_attn_summary", (batch.num_requests * (segs * per + heads * key_dim * value_dim),),
-                                torch.float32)
+        summary = workspace.get("lin_attn_summary", (batch.num_requests * segs * per,), torch.float32)
     lib = build.load_library("linear_attention")
     _call(lib, lib.tllm_linear_attention_scan, _ptr(q), _ptr(k), _ptr(v), q.stride(0), k.stride(0), v.stride(0),
           _ptr(head_decay), _ptr(gate), 0 if gate is None else gate.stride(0), _ptr(gate_bias), ctypes.c_float(inv_tau),
@@ -439,6 +438,16 @@ class _WinArgs(ctypes.Structure):
                 ("window", ctypes.c_int), ("pool", ctypes.c_int), ("fv", ctypes.c_void_p), ("n_tokens", ctypes.c_int)]
 
 
+# bfloat16 window attention on the tensor cores (0: the CUDA-core kernel, for comparisons)
+window_attention_tc = os.environ.get("TLLM_WINDOW_ATTENTION_TC", "1") != "0"
+
+
+def _keep(struct):
+    """A by-reference argument that stays valid for as long as a tape of launches holds it."""
+    ref = ctypes.byref(struct)
+    return ref
+
+
 def window_pool_attention(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int,
                           k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                           pool_k: Optional[torch.Tensor], pool_v: Optional[torch.Tensor],
@@ -480,8 +489,17 @@ def window_pool_attention(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, 
     a.positions, a.token_request, a.out = batch.positions.data_ptr(), batch.token_request.data_ptr(), out.data_ptr()
     a.scale, a.cap, a.head_bias = scale, (softcap or 0.0), head_bias.data_ptr()
     a.window, a.pool, a.fv, a.n_tokens = (window or 0), (pool or 0), (None if freq_v is None else freq_v.data_ptr()), t
+    heads_per_kv = num_heads // num_kv_heads
+    if qkv.dtype == torch.bfloat16 and window_attention_tc and not force_generic and key_dim % 16 == 0 and \
+            value_dim % 16 == 0 and key_dim <= 128 and value_dim <= 128 and heads_per_kv <= 64 and qkv.stride(0) % 8 == 0 and \
+            qkv.data_ptr() % 16 == 0 and getattr(batch, "cu_q", None) is not None:
+        # bfloat16: the tensor-core kernel compiled for this pair of sizes (prompt portions and decoded tokens alike)
+        lib = build.load_library("window_attention_mma", flags=(f"-DTLLM_HEAD_DIM={key_dim}", f"-DTLLM_VALUE_DIM={value_dim}"))
+        _call(lib, lib.tllm_window_pool_attention_mma, _keep(a), _ptr(batch.cu_q), _ptr(batch.q_start), batch.num_requests,
+              batch.max_q_len, _stream())
+        return
     lib = build.load_library("window_attention")
-    _call(lib, lib.tllm_window_pool_attention, ctypes.byref(a), _code(qkv.dtype), _stream())
+    _call(lib, lib.tllm_window_pool_attention, _keep(a), _code(qkv.dtype), _stream())
 
 
 def gelu(x: torch.Tensor, out: torch.Tensor) -> None:
@@ -1068,6 +1086,9 @@ ATTENTION_TC_HEAD_DIMS = (64, 128)            # head sizes the tcgen05 prompt-at
 ATTENTION_MAPS_DIMS = ((64, 128),)            # (key size, value size) pairs of the multi-map kernel compiled ahead
 
 
+WINDOW_ATTENTION_DIMS = ((64, 128),)   # (key size, value size) pairs of the window attention built ahead; others on first use
+
+
 def build_all(verbose: bool = True):
     """Compiles every library (what `__graft_entry__.build()` calls); returns their paths."""
     paths = [build.compile_library(n, verbose=verbose) for n in ALL_LIBRARIES]
@@ -1077,4 +1098,6 @@ def build_all(verbose: bool = True):
               for hd in ATTENTION_TC_HEAD_DIMS]
     paths += [build.compile_library("attention_maps_mma", flags=(f"-DTLLM_HEAD_DIM={kd}", f"-DTLLM_VALUE_DIM={vd}"), verbose=verbose)
               for kd, vd in ATTENTION_MAPS_DIMS]
+    paths += [build.compile_library("window_attention_mma", flags=(f"-DTLLM_HEAD_DIM={kd}", f"-DTLLM_VALUE_DIM={vd}"), verbose=verbose)
+              for kd, vd in WINDOW_ATTENTION_DIMS]
     return paths

@@ -25,7 +25,8 @@ HEADERS = ["common.cuh"]
 EXTRA_HEADERS = {"sampling": ["sampling_noalloc.h"], "attention_mma": ["attention_tiles.cuh"],
                  "attention_maps_mma": ["attention_tiles.cuh"],
                  "linear_tc": ["tc_common.cuh"],
-                 "attention_tc": ["tc_common.cuh"]}   # per-source headers that enter the hash
+                 "attention_tc": ["tc_common.cuh"],
+                 "window_attention": ["window_attention.cuh"], "window_attention_mma": ["window_attention.cuh"]}   # per-source headers that enter the hash
 
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
