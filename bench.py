@@ -671,7 +671,7 @@ def zozenex_kernels(dtype, device, pk, tokens=2048):
     corr = torch.zeros(experts, device=device)
     ids = torch.empty(t, top, dtype=torch.int32, device=device)
     wts = torch.empty(t, top, device=device)
-    tile = ops.moe_tile_rows(t * top, experts)
+    tile = ops.moe_tile_rows(t * top, experts, tensor_cores=dtype == torch.bfloat16)
     tiles = ops.moe_max_tiles(t * top, experts, tile)
     rows = torch.empty(tiles * tile, dtype=torch.int32, device=device)
     texp = torch.empty(tiles, dtype=torch.int32, device=device)

@@ -286,7 +286,8 @@ def test_router(experts, top, t):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("experts,top,t,h,ff", [(3, 3, 5, 48, 16), (16, 4, 300, 64, 40), (6, 2, 1, 96, 72), (9, 1, 130, 40, 8)])
+@pytest.mark.parametrize("experts,top,t,h,ff", [(3, 3, 5, 48, 16), (16, 4, 300, 64, 40), (6, 2, 1, 96, 72), (9, 1, 130, 40, 8),
+                                                  (4, 2, 450, 72, 136)])
 def test_grouped_expert_products(dtype, experts, top, t, h, ff):
     from tiny_llm_b200 import ops
     g = torch.Generator().manual_seed(7)
@@ -296,7 +297,7 @@ def test_grouped_expert_products(dtype, experts, top, t, h, ff):
     if t > 100:
         ids[:, 0] = 1                  # one expert gets a row of every token: several tiles
     wts = torch.rand(t, top, generator=g)
-    tile = ops.moe_tile_rows(t * top, experts)
+    tile = ops.moe_tile_rows(t * top, experts, tensor_cores=dtype == torch.bfloat16)
     tiles = ops.moe_max_tiles(t * top, experts, tile)
     rows = torch.empty(tiles * tile, dtype=torch.int32, device=DEV)
     texp = torch.empty(tiles, dtype=torch.int32, device=DEV)

@@ -108,28 +108,49 @@ __global__ void __launch_bounds__(512) linear_attention_scan_kernel(ScanArgs a) 
       else s[c][i] = ok ? su[(size_t)row * a.vd + col[c]] : 0.f;
     }
   }
-  for (int tb = t0; tb < t1; tb += LA_TOK) {
+  // The next tile's values are fetched into registers while the current tile is walked: NST staged elements of
+  // each of q, k (and the gate) and LA_TOK values of each column per thread.
+  constexpr int NST = LA_TOK * LA_ROWS / 32;
+  float rq[NST], rk[NST], rz[NST], vn[LA_CPT][LA_TOK];
+  auto fetch = [&](int tb) {
     const int nt = min(LA_TOK, t1 - tb);
-    for (int idx = tid; idx < LA_TOK * kdp; idx += nthreads) {
+#pragma unroll
+    for (int x = 0; x < NST; ++x) {
+      const int idx = tid + x * nthreads;
       const int tt = idx / kdp, row = idx % kdp;
-      float qv = 0.f, kv = 0.f, av = 1.f;
+      rq[x] = rk[x] = rz[x] = 0.f;
       if (tt < nt && row < a.kd) {
         const size_t t = (size_t)(tb + tt);
-        qv = to_f32(q[t * a.ldq + h * a.kd + row]) * a.q_scale;
-        kv = to_f32(k[t * a.ldk + h * a.kd + row]) * a.k_scale;
-        if (GATED) av = gate_decay(a.gate[t * a.ldg + h * a.kd + row] + a.gate_bias[h * a.kd + row], a.inv_tau);
+        rq[x] = to_f32(q[t * a.ldq + h * a.kd + row]);
+        rk[x] = to_f32(k[t * a.ldk + h * a.kd + row]);
+        if (GATED) rz[x] = a.gate[t * a.ldg + h * a.kd + row] + a.gate_bias[h * a.kd + row];
       }
-      sq[idx] = qv;
-      sk[idx] = kv;
-      if (GATED) sa[idx] = av;
+    }
+#pragma unroll
+    for (int tt = 0; tt < LA_TOK; ++tt)
+#pragma unroll
+      for (int c = 0; c < LA_CPT; ++c)
+        vn[c][tt] = (tt < nt && col_ok[c]) ? to_f32(v[(size_t)(tb + tt) * a.ldv + h * a.vd + col[c]]) : 0.f;
+  };
+  fetch(t0);
+  for (int tb = t0; tb < t1; tb += LA_TOK) {
+    const int nt = min(LA_TOK, t1 - tb);
+#pragma unroll
+    for (int x = 0; x < NST; ++x) {
+      const int idx = tid + x * nthreads;
+      const int tt = idx / kdp, row = idx % kdp;
+      const bool in = tt < nt && row < a.kd;
+      sq[idx] = rq[x] * a.q_scale;
+      sk[idx] = rk[x] * a.k_scale;
+      if (GATED) sa[idx] = in ? gate_decay(rz[x], a.inv_tau) : 1.f;
     }
     float vv[LA_CPT][LA_TOK];
 #pragma unroll
     for (int tt = 0; tt < LA_TOK; ++tt)
 #pragma unroll
-      for (int c = 0; c < LA_CPT; ++c)
-        vv[c][tt] = (tt < nt && col_ok[c]) ? to_f32(v[(size_t)(tb + tt) * a.ldv + h * a.vd + col[c]]) : 0.f;
+      for (int c = 0; c < LA_CPT; ++c) vv[c][tt] = vn[c][tt];
     __syncthreads();
+    if (tb + LA_TOK < t1) fetch(tb + LA_TOK);
 #pragma unroll
     for (int tt = 0; tt < LA_TOK; ++tt) {
       if (tt < nt) {
@@ -210,12 +231,25 @@ __global__ void linear_attention_prefix_kernel(ScanArgs a) {
   for (int e = blockIdx.x * blockDim.x + threadIdx.x; e < a.kd * a.vd; e += gridDim.x * blockDim.x) {
     const int row = e / a.vd;
     float x = st[e];
-    for (int g = 0; g < nseg; ++g) {
-      float* su = a.summary + (((size_t)r * a.max_segs + g) * a.heads + h) * per;
-      const bool more = g + 1 < nseg;
-      const float b = more ? su[e] : 0.f, d = more ? su[(size_t)a.kd * a.vd + row] : 0.f;
-      su[e] = x;
-      x = fmaf(d, x, b);
+    // eight segments' summaries are fetched before the first of them is overwritten
+    for (int g0 = 0; g0 < nseg; g0 += 8) {
+      float b[8], d[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int g = g0 + u;
+        const bool more = g + 1 < nseg;
+        const float* su = a.summary + (((size_t)r * a.max_segs + (more ? g : 0)) * a.heads + h) * per;
+        b[u] = more ? su[e] : 0.f;
+        d[u] = more ? su[(size_t)a.kd * a.vd + row] : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int g = g0 + u;
+        if (g < nseg) {
+          a.summary[(((size_t)r * a.max_segs + g) * a.heads + h) * per + e] = x;
+          x = fmaf(d[u], x, b[u]);
+        }
+      }
     }
   }
 }

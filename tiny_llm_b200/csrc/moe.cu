@@ -165,7 +165,8 @@ __global__ void __launch_bounds__(256) moe_linear_kernel(const T* __restrict__ i
 // ---- the grouped product on the tensor cores (bfloat16, mma.sync.m16n8k16, 32-bit sums)
 // A CTA owns BM rows of one expert's tile and 128 output columns; k in slices of 32 through a three- or four-stage cp.async
 // ring (rows of 80 bytes in shared memory: ldmatrix reads eight of them without a bank conflict).  Eight warps:
-// 2 x 4 of 32 x 32 outputs for tiles of 64 rows, 1 x 8 of 16 x 16 for tiles of 16 rows (decode).  A rows are
+// 2 x 4 of 64 x 32 outputs for tiles of 128 rows, of 32 x 32 for tiles of 64 rows, 1 x 8 of 16 x 16 for tiles of 16
+// rows (decode).  A rows are
 // gathered by the tile's row list; rows of padding read nothing.  K and the row strides are multiples of 8.
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
   const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -187,13 +188,17 @@ __global__ void __launch_bounds__(256) moe_linear_mma_kernel(const __nv_bfloat16
                                                              const int* __restrict__ sorted_rows,
                                                              const int* __restrict__ tile_expert, TO* __restrict__ out,
                                                              int n, int k, int rows_per_input) {
-  constexpr int BN = 128, BK = 32, LDS = 40, STAGES = BM == 64 ? 3 : 4;
-  constexpr int WM = BM == 64 ? 2 : 1, WN = 8 / WM;           // warps along rows and columns
-  constexpr int WTM = BM / WM, WTN = BN / WN;                 // a warp's outputs: 32 x 32 or 16 x 16
+  constexpr int BN = 128, BK = 32, LDS = 40, STAGES = BM == 16 ? 4 : 3;
+  constexpr int WM = BM >= 64 ? 2 : 1, WN = 8 / WM;           // warps along rows and columns
+  constexpr int WTM = BM / WM, WTN = BN / WN;                 // a warp's outputs: 64 x 32, 32 x 32 or 16 x 16
   constexpr int MI = WTM / 16, NI = WTN / 8;
-  __shared__ __align__(16) __nv_bfloat16 sa[STAGES][BM][LDS];
-  __shared__ __align__(16) __nv_bfloat16 sb[STAGES][BN][LDS];
-  __shared__ int srow[BM];
+  constexpr int A_PER_THREAD = (BM * 4 + 255) / 256;          // 16-byte pieces of A per thread and stage
+  extern __shared__ __align__(16) unsigned char moe_smem[];
+  typedef __nv_bfloat16 (*TileA)[BM][LDS];
+  typedef __nv_bfloat16 (*TileB)[BN][LDS];
+  TileA sa = reinterpret_cast<TileA>(moe_smem);
+  TileB sb = reinterpret_cast<TileB>(moe_smem + sizeof(__nv_bfloat16) * STAGES * BM * LDS);
+  int* srow = reinterpret_cast<int*>(moe_smem + sizeof(__nv_bfloat16) * STAGES * (BM + BN) * LDS);
   pdl_trigger();
   pdl_wait();
   const int e = tile_expert[blockIdx.x];
@@ -203,17 +208,26 @@ __global__ void __launch_bounds__(256) moe_linear_mma_kernel(const __nv_bfloat16
   if (tid < BM) srow[tid] = sorted_rows[(size_t)blockIdx.x * BM + tid];
   __syncthreads();
   const __nv_bfloat16* we = w + (size_t)e * n * k;
-  // what this thread copies per stage: one 16-byte piece of A (the first BM * 4 threads), two of B
-  const int a_row = tid >> 2, a_c = (tid & 3) * 8;
-  const bool a_mine = tid < BM * 4;
-  const int a_src = a_mine ? srow[a_row] : -1;
-  const __nv_bfloat16* a_ptr = in + (size_t)(a_src < 0 ? 0 : a_src / rows_per_input) * ld_in + a_c;
+  // what this thread copies per stage: its 16-byte pieces of A (BM * 4 in all) and two of B
+  const __nv_bfloat16* a_ptr[A_PER_THREAD];
+  bool a_ok[A_PER_THREAD];
+#pragma unroll
+  for (int x = 0; x < A_PER_THREAD; ++x) {
+    const int idx = tid + x * 256;
+    const int src = idx < BM * 4 ? srow[idx >> 2] : -1;
+    a_ok[x] = src >= 0;
+    a_ptr[x] = in + (size_t)(src < 0 ? 0 : src / rows_per_input) * ld_in + (idx & 3) * 8;
+  }
   const int nk = (k + BK - 1) / BK;
   auto load = [&](int stage, int kb) {
     const int k0 = kb * BK;
-    if (a_mine) {
-      const bool ok = a_src >= 0 && k0 + a_c < k;
-      cp_async16(&sa[stage][a_row][a_c], a_ptr + (ok ? k0 : 0), ok);
+#pragma unroll
+    for (int x = 0; x < A_PER_THREAD; ++x) {
+      const int idx = tid + x * 256, c = (idx & 3) * 8;
+      if (idx < BM * 4) {
+        const bool ok = a_ok[x] && k0 + c < k;
+        cp_async16(&sa[stage][idx >> 2][c], a_ptr[x] + (ok ? k0 : 0), ok);
+      }
     }
 #pragma unroll
     for (int x = 0; x < 2; ++x) {
@@ -340,25 +354,36 @@ static int moe_linear_launch(const void* in, int ld_in, const void* w, const int
 extern "C" int tllm_moe_linear(const void* in, int ld_in, const void* w, const int* sorted_rows, const int* tile_expert,
                                void* out, int n, int k, int rows_per_input, int tile, int max_tiles, int gelu, int dtype,
                                int out_dtype, int use_mma, void* stream) {
-  TLLM_REQUIRE(n > 0 && k > 0 && rows_per_input > 0 && max_tiles > 0 && (tile == 16 || tile == 64), "moe_linear: sizes do not fit (tile %d)", tile);
+  TLLM_REQUIRE(n > 0 && k > 0 && rows_per_input > 0 && max_tiles > 0 && (tile == 16 || tile == 64 || tile == 128), "moe_linear: sizes do not fit (tile %d)", tile);
+  TLLM_REQUIRE(tile != 128 || (dtype == TLLM_BF16 && use_mma && k % 8 == 0 && ld_in % 8 == 0 && ((uintptr_t)in & 15) == 0 && ((uintptr_t)w & 15) == 0),
+               "moe_linear: tiles of 128 rows are the tensor-core kernel's");
   TLLM_REQUIRE(max_tiles <= 2147483647 && (n + 63) / 64 <= 65535, "moe_linear: the grid is too large");
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == TLLM_BF16 && use_mma && k % 8 == 0 && ld_in % 8 == 0 && ((uintptr_t)in & 15) == 0 && ((uintptr_t)w & 15) == 0) {
     const dim3 grid((unsigned)max_tiles, (unsigned)((n + 127) / 128));
     TLLM_REQUIRE((n + 127) / 128 <= 65535, "moe_linear: the grid is too large");
 #define TLLM_MOE_MMA(TO, BM, G)                                                                                           \
-  TLLM_LAUNCH("moe_linear", (moe_linear_mma_kernel<TO, BM, G>), grid, 256, 0, s, (const __nv_bfloat16*)in, ld_in,          \
-              (const __nv_bfloat16*)w, sorted_rows, tile_expert, (TO*)out, n, k, rows_per_input)
-    if (out_dtype == TLLM_BF16) {
-      if (tile == 16) { if (gelu) TLLM_MOE_MMA(__nv_bfloat16, 16, true); else TLLM_MOE_MMA(__nv_bfloat16, 16, false); }
-      else { if (gelu) TLLM_MOE_MMA(__nv_bfloat16, 64, true); else TLLM_MOE_MMA(__nv_bfloat16, 64, false); }
-      return TLLM_OK;
-    }
-    if (out_dtype == TLLM_F32) {
-      if (tile == 16) { if (gelu) TLLM_MOE_MMA(float, 16, true); else TLLM_MOE_MMA(float, 16, false); }
-      else { if (gelu) TLLM_MOE_MMA(float, 64, true); else TLLM_MOE_MMA(float, 64, false); }
-      return TLLM_OK;
-    }
+  do {                                                                                                                    \
+    const size_t smem = sizeof(__nv_bfloat16) * (BM == 16 ? 4 : 3) * (BM + 128) * 40 + BM * sizeof(int);                   \
+    static bool configured = false;                                                                                       \
+    if (!configured) {                                                                                                    \
+      cudaError_t e_ = cudaFuncSetAttribute(moe_linear_mma_kernel<TO, BM, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      if (e_ != cudaSuccess) TLLM_FAIL(TLLM_ERR_CUDA, "moe_linear: %s", cudaGetErrorString(e_));                           \
+      configured = true;                                                                                                  \
+    }                                                                                                                     \
+    TLLM_LAUNCH("moe_linear", (moe_linear_mma_kernel<TO, BM, G>), grid, 256, smem, s, (const __nv_bfloat16*)in, ld_in,     \
+                (const __nv_bfloat16*)w, sorted_rows, tile_expert, (TO*)out, n, k, rows_per_input);                        \
+  } while (0)
+#define TLLM_MOE_MMA_TILES(TO)                                                                      \
+  do {                                                                                              \
+    if (tile == 16) { if (gelu) TLLM_MOE_MMA(TO, 16, true); else TLLM_MOE_MMA(TO, 16, false); }      \
+    else if (tile == 64) { if (gelu) TLLM_MOE_MMA(TO, 64, true); else TLLM_MOE_MMA(TO, 64, false); } \
+    else { if (gelu) TLLM_MOE_MMA(TO, 128, true); else TLLM_MOE_MMA(TO, 128, false); }               \
+    return TLLM_OK;                                                                                 \
+  } while (0)
+    if (out_dtype == TLLM_BF16) TLLM_MOE_MMA_TILES(__nv_bfloat16);
+    if (out_dtype == TLLM_F32) TLLM_MOE_MMA_TILES(float);
+#undef TLLM_MOE_MMA_TILES
 #undef TLLM_MOE_MMA
   }
   if (dtype == TLLM_F32 && out_dtype == TLLM_F32)

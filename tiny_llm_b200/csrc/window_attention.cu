@@ -115,12 +115,16 @@ __global__ void pool_kv_blocks_kernel(const T* __restrict__ kcache, const T* __r
     float sum = 0.f;
     // eight loads in flight, added in the order of the positions
     for (int j0 = first; j0 <= p; j0 += 8) {
+      long long pg[8];
       float x[8];
 #pragma unroll
+      for (int u = 0; u < 8; ++u) pg[u] = table[min(j0 + u, p) / page_size];
+#pragma unroll
       for (int u = 0; u < 8; ++u) {
-        const int j = j0 + u;
-        const long long page = j <= p ? table[j / page_size] : -1;   // a token's page outlives its block's completion
-        x[u] = page >= 0 ? to_f32(base[page * page_stride + (long long)(j % page_size) * row]) : 0.f;
+        const int j = min(j0 + u, p);
+        // a token's page outlives its block's completion; a missing one (never) would read page 0 and count as zero
+        x[u] = to_f32(base[(pg[u] < 0 ? 0 : pg[u]) * page_stride + (long long)(j % page_size) * row]);
+        if (j0 + u > p || pg[u] < 0) x[u] = 0.f;
       }
 #pragma unroll
       for (int u = 0; u < 8; ++u) sum += x[u];

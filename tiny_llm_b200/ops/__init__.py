@@ -527,9 +527,12 @@ def moe_route(logits: torch.Tensor, num_experts: int, correction: torch.Tensor, 
           _ptr(ids), _ptr(weights), t, _stream())
 
 
-def moe_tile_rows(pairs: int, num_experts: int) -> int:
-    """Rows per tile of the grouped product: 16 while an expert gets few rows (decode), else 64."""
-    return 16 if pairs <= 16 * num_experts else 64
+def moe_tile_rows(pairs: int, num_experts: int, tensor_cores: bool = False) -> int:
+    """Rows per tile of the grouped product: 16 while an expert gets few rows (decode), else 64; 128 where the
+    tensor-core kernel runs and an expert gets some hundred rows."""
+    if pairs <= 16 * num_experts:
+        return 16
+    return 128 if tensor_cores and moe_mma and not force_generic and pairs >= 192 * num_experts else 64
 
 
 def moe_max_tiles(pairs: int, num_experts: int, tile: int) -> int:

@@ -64,7 +64,8 @@ class RoutedExperts:
         ids = ws.get("moe_ids", (t, top), torch.int32)
         weights = ws.get("moe_weights", (t, top), torch.float32)
         ops.moe_route(logits, n, self.correction, self.route_scale, ids, weights)
-        tile = ops.moe_tile_rows(t * top, n)
+        tile = ops.moe_tile_rows(t * top, n, tensor_cores=(ctx.dtype == torch.bfloat16 and self.hidden_size % 8 == 0 and
+                                                             self.expert_size % 8 == 0))
         tiles = ops.moe_max_tiles(t * top, n, tile)
         sorted_rows = ws.get("moe_rows", (tiles * tile,), torch.int32)
         tile_expert = ws.get("moe_tile_expert", (tiles,), torch.int32)
