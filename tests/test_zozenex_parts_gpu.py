@@ -288,8 +288,9 @@ def test_router(experts, top, t):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("experts,top,t,h,ff", [(3, 3, 5, 48, 16), (16, 4, 300, 64, 40), (6, 2, 1, 96, 72), (9, 1, 130, 40, 8),
                                                   (4, 2, 450, 72, 136)])
-def test_grouped_expert_products(dtype, experts, top, t, h, ff):
+def test_grouped_expert_products(dtype, experts, top, t, h, ff, monkeypatch):
     from tiny_llm_b200 import ops
+    monkeypatch.setattr(ops, "moe_wide_tiles", True)     # tiles of 128 rows too, where an expert gets enough rows
     g = torch.Generator().manual_seed(7)
     x = torch.randn(t, h, generator=g).to(dtype)
     up, down = (torch.randn(experts, ff, h, generator=g) * 0.2).to(dtype), (torch.randn(experts, h, ff, generator=g) * 0.2).to(dtype)

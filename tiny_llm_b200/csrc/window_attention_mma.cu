@@ -178,9 +178,9 @@ __global__ void __launch_bounds__(NTHREADS) window_pool_attention_mma_kernel(Win
         if (code >= 0) vis = code <= i && (W <= 0 || i - code < W);
         else vis = code != NO_KEY && (-code - 1) <= i - W;
         float x = s[j][c] * scale;
-        if (cap > 0.f) x = cap * (1.f - 2.f / (1.f + __expf(2.f * x * inv_cap)));   // cap tanh(x / cap)
+        if (cap > 0.f) x = cap * (1.f - __fdividef(2.f, 1.f + __expf(2.f * x * inv_cap)));   // cap tanh(x / cap)
         x += c < 2 ? bA : bB;
-        p[c] = vis ? 1.f / (1.f + __expf(-x)) : 0.f;
+        p[c] = vis ? __fdividef(1.f, 1.f + __expf(-x)) : 0.f;   // the hardware's exp2 and reciprocal, 32-bit, about 2^-21
       }
       split2(p[0], p[1], phi[j][0], plo[j][0]);
       split2(p[2], p[3], phi[j][1], plo[j][1]);

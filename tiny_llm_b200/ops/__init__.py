@@ -97,7 +97,7 @@ def replay_tape(tape) -> None:
 def knobs():
     """The module's switches that decide which kernels a step launches; a tape or graph holds for one setting of them."""
     return (force_generic, split_k, cluster_mask, attention_tc, decode_wide_ctas, decode_cluster_merge, qkv_fused_rows,
-            linear_skinny, generic_attention_split, split_mixed_attention, min_gru_segment, linear_attention_segment, moe_mma, window_attention_tc, attention_maps_tc, attention_maps_decode_pairs, _pdl)
+            linear_skinny, generic_attention_split, split_mixed_attention, min_gru_segment, linear_attention_segment, moe_mma, moe_wide_tiles, window_attention_tc, attention_maps_tc, attention_maps_decode_pairs, _pdl)
 
 
 def _i32(t: Optional[torch.Tensor], name: str):
@@ -532,7 +532,7 @@ def moe_tile_rows(pairs: int, num_experts: int, tensor_cores: bool = False) -> i
     tensor-core kernel runs and an expert gets some hundred rows."""
     if pairs <= 16 * num_experts:
         return 16
-    return 128 if tensor_cores and moe_mma and not force_generic and pairs >= 192 * num_experts else 64
+    return 128 if tensor_cores and moe_mma and not force_generic and moe_wide_tiles and pairs >= 192 * num_experts else 64
 
 
 def moe_max_tiles(pairs: int, num_experts: int, tile: int) -> int:
@@ -556,6 +556,9 @@ def moe_align(ids: torch.Tensor, num_experts: int, tile: int, sorted_rows: torch
 
 # bfloat16 grouped products on the tensor cores (0: the FFMA kernel, for comparisons)
 moe_mma = os.environ.get("TLLM_MOE_MMA", "1") != "0"
+# tiles of 128 rows where an expert gets some hundred rows: measured no faster than tiles of 64 (240 against 225 us for
+# 8,192 rows of 2,048 x 1,408) and they pad more, so they are off unless asked for
+moe_wide_tiles = os.environ.get("TLLM_MOE_TILE_128", "0") == "1"
 
 
 def moe_linear(a: torch.Tensor, w: torch.Tensor, sorted_rows: torch.Tensor, tile_expert: torch.Tensor, tile: int,
