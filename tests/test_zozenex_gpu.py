@@ -11,7 +11,8 @@ from zozenex_util import ZOZ, compare, plain_logits, plain_model, tolerances, wr
 
 pytestmark = pytest.mark.gpu
 DTYPES = ["float32", "bfloat16"]
-LENGTHS = {"A": [100, 64, 33, 47, 130, 17, 2, 51], "B": [97, 1, 40, 200, 33, 64, 13, 150], "C": [70, 90, 35, 49, 8]}
+LENGTHS = {"A": [100, 64, 33, 47, 130, 17, 2, 51], "B": [97, 1, 40, 200, 33, 64, 13, 150], "C": [70, 90, 35, 49, 8],
+           "D": [61, 5, 44, 90, 23]}
 
 
 @pytest.fixture(scope="module")
@@ -38,7 +39,7 @@ def runner_for(model_dir, dtype, page, max_tokens, max_requests=4, poison=True, 
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 @pytest.mark.parametrize("how", ["whole", "tail", "portions", "mixed"])
 def test_replay_in_process(cases, name, dtype, how):
     model_dir, cfg, page, reqs, ref, tol = cases[name]
@@ -67,7 +68,7 @@ def test_trace_run_program(cases, name, dtype):
     compare(got, ref[dtype], "m", tol[dtype], f"zozenex {name} mixed (program) {dtype}")
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_cuts_batches_and_pages_do_not_move_the_32_bit_logits(cases, name):
     """Whole, portions, and mixed batches with other page sizes and pools: the 32-bit path gives the same bits."""
     model_dir, cfg, page, reqs, ref, tol = cases[name]

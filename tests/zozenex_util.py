@@ -67,7 +67,17 @@ ZOZ_C = {
         parallel(left(1, 1, 16, 6, 0.3, rot=(16, 50.0)), right(4, 4, 12, 1.5, rank=3), moe(7, 4, 8, 3.0)),
     ],
 }
-ZOZ = {"A": (ZOZ_A, 16, 3), "B": (ZOZ_B, 8, 4), "C": (ZOZ_C, 4, 5)}   # config, page size, seed
+# sizes that are multiples of nothing convenient: a width of 44, keys of 6 and 10, values of 10 and 14, a vocabulary of 97
+ZOZ_D = {
+    "architecture": "Zozenex", "vocab": 97, "width": 44, "max_positions": 300, "norm": {"eps": 1e-5},
+    "initializer_range": 0.12,
+    "layers": [
+        retention(3, 6, 10, [0.5, 0.9, 0.99], moe(5, 2, 12, 1.2, shared=20)),
+        parallel(left(3, 3, 10, 14, 0.35, softcap=8.0, size=11, pool=4, rot=(6, 20.0)), right(2, 6, 6, 2.0, rank=2),
+                 moe(2, 1, 6, 0.9)),
+    ],
+}
+ZOZ = {"A": (ZOZ_A, 16, 3), "B": (ZOZ_B, 8, 4), "C": (ZOZ_C, 4, 5), "D": (ZOZ_D, 4, 6)}   # config, page size, seed
 
 
 def write_models(tmp_path_factory):
