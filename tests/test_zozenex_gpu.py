@@ -68,6 +68,20 @@ def test_trace_run_program(cases, name, dtype):
     compare(got, ref[dtype], "m", tol[dtype], f"zozenex {name} mixed (program) {dtype}")
 
 
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_prompt_portions_through_the_tcgen05_grouped_product(cases, name, monkeypatch):
+    """With the threshold lowered, every prompt portion that has at least a row per expert sends its experts' rows
+    through the contiguous grouped order and the tcgen05 product (decoded tokens keep the gathering kernel)."""
+    from tiny_llm_b200 import ops
+    monkeypatch.setattr(ops, "moe_tc_rows_per_expert", 1)
+    model_dir, cfg, page, reqs, ref, tol = cases[name]
+    for steps, prefix in ((ru.trace_whole(reqs), "w"), (ru.trace_tail(reqs), "t"), (ru.trace_mixed(reqs, 4), "m")):
+        runner = runner_for(model_dir, "bfloat16", page, ru.tokens_needed(steps, round_to=page))
+        got = ru.run_trace_runner(runner, steps, cfg["vocab"])
+        compare(got, ref["bfloat16"], prefix, tol["bfloat16"], f"zozenex {name} {prefix} tcgen05 experts")
+    ops.check_status()
+
+
 @pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_cuts_batches_and_pages_do_not_move_the_32_bit_logits(cases, name):
     """Whole, portions, and mixed batches with other page sizes and pools: the 32-bit path gives the same bits."""

@@ -331,6 +331,44 @@ def test_grouped_expert_products(dtype, experts, top, t, h, ff, monkeypatch):
     assert float((out2.cpu().double() + torch.sigmoid(logit[:, 3:4].double()) * shared.double() - ref).abs().max()) <= tol
 
 
+@pytest.mark.parametrize("experts,top,t,h,ff", [(3, 3, 5, 48, 16), (16, 4, 300, 64, 40), (6, 2, 130, 96, 72), (5, 1, 700, 40, 264)])
+def test_grouped_expert_products_on_tcgen05(experts, top, t, h, ff):
+    """The same products through the contiguous grouped order and the tcgen05 kernel: every tile of 128 rows reads its
+    own expert's rows of the stacked weights, tiles that do not exist are skipped, padding rows cost nothing."""
+    from tiny_llm_b200 import ops
+    g = torch.Generator().manual_seed(9)
+    dtype = torch.bfloat16
+    x = torch.randn(t, h, generator=g).to(dtype)
+    up, down = (torch.randn(experts, ff, h, generator=g) * 0.2).to(dtype), (torch.randn(experts, h, ff, generator=g) * 0.2).to(dtype)
+    ids = torch.stack([torch.randperm(experts, generator=g)[:top] for _ in range(t)]).to(torch.int32)
+    if experts > 4:
+        ids[ids == 2] = 3              # an expert that nobody chooses: its tiles do not exist
+    wts = torch.rand(t, top, generator=g)
+    tile = ops.MOE_TC_TILE
+    tiles = ops.moe_max_tiles(t * top, experts, tile)
+    rows = torch.empty(tiles * tile, dtype=torch.int32, device=DEV)
+    texp = torch.empty(tiles, dtype=torch.int32, device=DEV)
+    pos = torch.empty(t * top, dtype=torch.int32, device=DEV)
+    ops.moe_align(ids.to(DEV), experts, tile, rows, texp, pos)
+    assert torch.equal(rows.cpu()[pos.cpu().long()], torch.arange(t * top, dtype=torch.int32))
+    grouped = torch.full((tiles * tile, h), float("nan"), dtype=dtype, device=DEV)
+    ops.moe_gather(x.to(DEV), rows, texp, tile, grouped, rows_per_input=top)
+    act = torch.full((tiles * tile, ff), float("nan"), dtype=dtype, device=DEV)
+    ops.moe_linear_tc(grouped, up.to(DEV), texp, act, gelu=True)
+    y = torch.full((tiles * tile, h), float("nan"), device=DEV)
+    ops.moe_linear_tc(act, down.to(DEV), texp, y)
+    ops.check_status()
+    resid = torch.randn(t, h, generator=g)
+    out = resid.clone().to(DEV)
+    ops.moe_combine(y, wts.to(DEV), None, None, 0, out, pos)
+    ref = resid.double()
+    for i in range(t):
+        for c in range(top):
+            e = int(ids[i, c])
+            ref[i] += wts[i, c].double() * (down[e].double() @ pz.bf16_quant(pz.gelu_erf(up[e].double() @ x[i].double())))
+    assert float((out.cpu().double() - ref).abs().max()) <= 2.0 ** -7 * float(ref.abs().max())
+
+
 def test_normed_branch_add_and_gelu():
     from tiny_llm_b200 import ops
     g = torch.Generator().manual_seed(8)

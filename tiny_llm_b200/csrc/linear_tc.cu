@@ -40,7 +40,8 @@ enum Epilogue { EPI_BF16 = 0, EPI_F32 = 1, EPI_ADD_F32 = 2, EPI_SWIGLU = 3, EPI_
                 // cluster kernel: K slices reduced through distributed shared memory
                 EPI_CL_ADD_F32 = 5, EPI_CL_ROPE_KV = 6, EPI_CL_SWIGLU = 7, EPI_CL_BF16 = 8,
                 // NORMAL orientation: Q/K/V projection with rotation and cache write (head size 64 or 128)
-                EPI_ROPE_KV = 9 };
+                EPI_ROPE_KV = 9,
+                EPI_GELU_BF16 = 10 };   // bfloat16 store of the exact GELU of the sums (the grouped expert product)
 
 constexpr int ERR_PRODUCER = 1, ERR_MMA = 2, ERR_EPILOGUE = 3;
 
@@ -73,6 +74,10 @@ struct ClusterArgs {
   // different CTAs add into the output (0 or 1: whole K per tile); fills the SMs when there are few tiles
   int k_splits, k_per;             // runs per tile and k-blocks per run (the last run may be shorter, never empty)
   int out_by_tma;                  // residual-adding epilogue: the sums leave as TMA reductions (the output's map is valid)
+  // persistent kernel, grouped product: row tile i of A belongs to expert tile_expert[i] (-1: no such tile, skipped by
+  // every role), whose weights are rows [expert * expert_rows, +rows_b) of the stacked B matrix (null: one B for all)
+  const int* tile_expert;
+  int expert_rows;
 };
 
 // Epilogue of one 128 x BN tile of C in the NORMAL orientation: this thread owns row `row` of the
@@ -154,7 +159,7 @@ __device__ __forceinline__ void store_tile_normal(uint32_t taddr, int row, int t
                                                   int rows_b, void* __restrict__ out, int ldo) {
   // 16-byte stores need an aligned base and row stride
   const bool vec_ok = (reinterpret_cast<uintptr_t>(out) & 15) == 0 &&
-                      ((EPI == EPI_BF16 || EPI == EPI_SWIGLU) ? (ldo & 7) == 0 : (ldo & 3) == 0);
+                      ((EPI == EPI_BF16 || EPI == EPI_GELU_BF16 || EPI == EPI_SWIGLU) ? (ldo & 7) == 0 : (ldo & 3) == 0);
   const int m = tile_a * BM + row;
   if (EPI == EPI_SWIGLU) {
     // columns [0, BN/2) are gate, [BN/2, BN) the matching up columns; output tile is BN/2 wide
@@ -192,7 +197,11 @@ __device__ __forceinline__ void store_tile_normal(uint32_t taddr, int row, int t
       tmem_ld32(taddr + c, v);
       if (m < rows_a && n0 + c < rows_b) {
         const bool full = n0 + c + 32 <= rows_b;
-        if (EPI == EPI_BF16) {
+        if (EPI == EPI_GELU_BF16) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0.5f * v[j] * (1.f + erff(v[j] * 0.70710678118654752440f));
+        }
+        if (EPI == EPI_BF16 || EPI == EPI_GELU_BF16) {
           __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)m * ldo + n0 + c;
           if (full && vec_ok) {
 #pragma unroll
@@ -769,6 +778,9 @@ linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     return (item_tile(i) / tiles_m) * BN + (i < whole ? 0 : ((i - whole) % strips) * (EPI == EPI_SWIGLU ? ca.tail_width / 2 : ca.tail_width));
   };
   auto item_width = [&](int i) { return i < whole ? BN : ca.tail_width; };
+  // grouped product: the expert of an item's row tile (read after the wait for earlier kernels, which write the list)
+  const bool grouped = ca.tile_expert != nullptr;
+  auto item_expert = [&](int i) { return grouped ? ca.tile_expert[item_tile(i) % tiles_m] : 0; };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -786,7 +798,8 @@ linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
   // before this grid waits for its predecessors.
   pdl_trigger();
   const int first_tile = blockIdx.x;
-  const int n_pre = first_tile < whole ? min(item_kbn(first_tile), STAGES) : 0;   // (a CTA's first item is a whole tile, or it has none worth the trouble)
+  // (a CTA's first item is a whole tile, or it has none worth the trouble; a grouped product learns its weights' rows later)
+  const int n_pre = (first_tile < whole && !grouped) ? min(item_kbn(first_tile), STAGES) : 0;
   if (warp == 0 && lane == 0) {
     const int tn = item_tile(first_tile) / tiles_m, kb0 = item_kb0(first_tile);
     for (int i = 0; i < n_pre; ++i) {
@@ -802,7 +815,9 @@ linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     int it = 0;   // k-blocks issued so far, over all tiles: stage = it % STAGES
     bool ok = true;
     for (int t = first_tile; t < n_items && ok; t += gridDim.x) {
-      const int tm = item_tile(t) % tiles_m, col = item_col(t), width = item_width(t);
+      const int ex = item_expert(t);
+      if (ex < 0) continue;
+      const int tm = item_tile(t) % tiles_m, col = item_col(t) + ex * ca.expert_rows, width = item_width(t);
       const int kb0 = item_kb0(t), kb1 = kb0 + item_kbn(t);
       for (int kb = kb0; kb < kb1; ++kb, ++it) {
         const int s = it % STAGES;
@@ -827,7 +842,8 @@ linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     const uint32_t lo0 = smem_desc_sw128_lo(smem_u32(smem));
     int it = 0, local = 0;
     bool ok = true;
-    for (int t = first_tile; t < n_items && ok; t += gridDim.x, ++local) {
+    for (int t = first_tile; t < n_items && ok; t += gridDim.x) {
+      if (item_expert(t) < 0) continue;
       const uint32_t idesc = instr_desc_bf16(BM, item_width(t));
       const int buf = local & 1;
       ok = __all_sync(0xffffffffu, mbar_wait(&acc_empty[buf], ((local >> 1) & 1) ^ 1, abort_flag));
@@ -852,6 +868,7 @@ linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       if (!ok) break;
       if (elect_one()) umma_commit(&acc_full[buf]);   // arrives when this tile's MMAs have completed
       __syncwarp();
+      ++local;
     }
     if (!ok && lane == 0) { *abort_flag = 1; atomicExch(status, ERR_MMA); }
   } else if (warp >= 2) {
@@ -860,7 +877,8 @@ linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
     const int row = quad * 32 + lane;
     int local = 0;
     int out_chunks = 0;   // staging chunks handed to the TMA unit so far (their buffers alternate)
-    for (int t = first_tile; t < n_items; t += gridDim.x, ++local) {
+    for (int t = first_tile; t < n_items; t += gridDim.x) {
+      if (item_expert(t) < 0) continue;
       const int buf = local & 1;
       bool ok = mbar_wait(&acc_full[buf], (local >> 1) & 1, abort_flag);
       if (!ok) { *abort_flag = 1; atomicExch(status, ERR_EPILOGUE); }
@@ -904,6 +922,7 @@ linear_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __g
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&acc_empty[buf]);   // four arrivals free the accumulator
+      ++local;
     }
     if (EPI == EPI_ADD_F32 && warp == 2 && lane == 0) bulk_wait_all();   // every reduction of this CTA has been performed
   }
@@ -1090,6 +1109,30 @@ using namespace tllm;
 //   swap: 0 = 128 x 256 tiles of C per CTA (large M); 1 = weights on the 128-row side, M <= 128,
 //        `splits` slices of K per weight tile (epi 4 when splits > 1).
 // `status` is a device int that receives a non-zero code if a bounded wait expired.
+// The grouped product of a mixture of experts: A [rows, k] holds whole tiles of 128 rows, every tile the rows of ONE
+// expert (tile_expert[rows / 128], -1 for a tile that does not exist); w is [experts * n, k], expert e's matrix in rows
+// [e n, (e + 1) n); out [rows, n]: bfloat16 of GELU(sums) (epi 10) or float32 sums (epi 1).
+extern "C" int tllm_linear_tc_grouped(const void* a, const void* w, void* out, int rows, int n, int k, int lda, int ldo,
+                                      int experts, const int* tile_expert, int epi, int* status, void* stream) {
+  TLLM_REQUIRE(rows > 0 && rows % BM == 0 && n > 0 && k > 0 && experts > 0, "linear_tc_grouped: %d rows (whole tiles of %d), %d x %d, %d experts", rows, BM, n, k, experts);
+  TLLM_REQUIRE(k % 8 == 0 && lda % 8 == 0, "linear_tc_grouped: K (%d) and the row stride of A (%d) must be multiples of 8 (16-byte rule of TMA)", k, lda);
+  TLLM_REQUIRE(((uintptr_t)a % 16) == 0 && ((uintptr_t)w % 16) == 0, "linear_tc_grouped: operands must be 16-byte aligned");
+  TLLM_REQUIRE(status != nullptr && tile_expert != nullptr, "linear_tc_grouped: needs a status word and the tiles' experts");
+  TLLM_REQUIRE((long long)experts * n <= 2147483647LL, "linear_tc_grouped: the stacked weights have too many rows");
+  CUtensorMap ma, mb;
+  if (!make_map(&ma, a, rows, k, lda, BM) || !make_map(&mb, w, experts * n, k, k, 256))
+    TLLM_FAIL(TLLM_ERR_CUDA, "linear_tc_grouped: cuTensorMapEncodeTiled failed");
+  ClusterArgs ca = ClusterArgs();
+  ca.tile_expert = tile_expert;
+  ca.expert_rows = n;
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (epi) {
+    case EPI_GELU_BF16: return launch_persistent<EPI_GELU_BF16>(ma, mb, out, rows, n, k, ldo, status, s, ca);
+    case EPI_F32: return launch_persistent<EPI_F32>(ma, mb, out, rows, n, k, ldo, status, s, ca);
+  }
+  TLLM_FAIL(TLLM_ERR_ARG, "linear_tc_grouped: epilogue %d (GELU to bfloat16 or float32 sums)", epi);
+}
+
 extern "C" int tllm_linear_tc(const void* a, const void* w, void* out, int m, int n, int k, int lda, int ldo, int epi,
                               int swap, int splits, int* status, void* stream) {
   TLLM_REQUIRE(m > 0 && n > 0 && k > 0, "linear_tc: empty product %d x %d x %d", m, n, k);

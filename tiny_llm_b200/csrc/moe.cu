@@ -10,7 +10,8 @@
 //   fmaf over ascending k, so a row's result does not depend on the tile it landed in) and mma.sync tiles for
 //   bfloat16 (below).
 // moe_combine: resid[t] += sum_c weight[t, c] * y[t * top + c] (+ sigmoid(gate logit) * shared[t]), choices in the
-//   order the router found them.
+//   order the router found them; with pair_pos, y is in the grouped order and pair p lies in row pair_pos[p].
+// moe_gather: the grouped order's input rows made contiguous (for a product that fetches A tiles by TMA).
 // gelu: the exact (erf) GELU, element by element.
 #include "common.cuh"
 
@@ -69,7 +70,7 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int ld, int n
 
 // One CTA.  Shared: counts[n_experts], start[n_experts] (ints).
 __global__ void moe_align_kernel(const int* __restrict__ ids, int n_pairs, int n_experts, int tile, int max_tiles,
-                                 int* __restrict__ sorted_rows, int* __restrict__ tile_expert) {
+                                 int* __restrict__ sorted_rows, int* __restrict__ tile_expert, int* __restrict__ pair_pos) {
   extern __shared__ int sh[];
   int* counts = sh;
   int* start = sh + n_experts;
@@ -96,8 +97,25 @@ __global__ void moe_align_kernel(const int* __restrict__ ids, int n_pairs, int n
   // does not depend on where in its expert's tiles it lies.
   for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
     const int e = ids[i];
-    sorted_rows[start[e] + atomicAdd(&counts[e], 1)] = i;
+    const int at = start[e] + atomicAdd(&counts[e], 1);
+    sorted_rows[at] = i;
+    if (pair_pos) pair_pos[i] = at;     // where the pair's row lies in the grouped order
   }
+}
+
+// The rows of a grouped order made contiguous: out[p] = in[sorted_rows[p] / rows_per_input], zeros for padding, so
+// that a product that fetches its A tiles by TMA can take them (16-byte pieces; k a multiple of 8).
+__global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ in, int ld_in, const int* __restrict__ sorted_rows,
+                                  const int* __restrict__ tile_expert, int tile, int rows_per_input,
+                                  __nv_bfloat16* __restrict__ out, int k) {
+  pdl_trigger();
+  pdl_wait();
+  const int p = blockIdx.x;
+  if (tile_expert[p / tile] < 0) return;      // a tile that does not exist is never read
+  const int src = sorted_rows[p];
+  const uint4* from = reinterpret_cast<const uint4*>(in + (size_t)(src < 0 ? 0 : src / rows_per_input) * ld_in);
+  uint4* to = reinterpret_cast<uint4*>(out + (size_t)p * k);
+  for (int c = threadIdx.x; c < k / 8; c += blockDim.x) to[c] = src < 0 ? make_uint4(0, 0, 0, 0) : from[c];
 }
 
 // Tile of TM rows x 64 columns, k in slices of 16; 256 threads, each TM/16 rows x 4 columns.
@@ -291,7 +309,7 @@ __global__ void __launch_bounds__(256) moe_linear_mma_kernel(const __nv_bfloat16
 
 __global__ void moe_combine_kernel(const float* __restrict__ y, const float* __restrict__ weights, int top,
                                    const float* __restrict__ shared, const float* __restrict__ logits, int ld_logits,
-                                   int gate_col, float* __restrict__ resid, int width) {
+                                   int gate_col, float* __restrict__ resid, int width, const int* __restrict__ pair_pos) {
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
@@ -299,7 +317,10 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const float* __r
   if (shared) g = 1.f / (1.f + expf(-logits[(size_t)t * ld_logits + gate_col]));
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
     float acc = 0.f;
-    for (int x = 0; x < top; ++x) acc = fmaf(weights[(size_t)t * top + x], y[((size_t)t * top + x) * width + c], acc);
+    for (int x = 0; x < top; ++x) {
+      const size_t pair = (size_t)t * top + x;
+      acc = fmaf(weights[pair], y[(pair_pos ? (size_t)pair_pos[pair] : pair) * width + c], acc);
+    }
     if (shared) acc = fmaf(g, shared[(size_t)t * width + c], acc);
     resid[(size_t)t * width + c] += acc;
   }
@@ -328,11 +349,22 @@ extern "C" int tllm_moe_route(const float* logits, int ld, int n_experts, const 
 }
 
 extern "C" int tllm_moe_align(const int* ids, int n_pairs, int n_experts, int tile, int max_tiles, int* sorted_rows,
-                              int* tile_expert, void* stream) {
+                              int* tile_expert, int* pair_pos, void* stream) {
   TLLM_REQUIRE(n_pairs > 0 && n_experts > 0 && tile > 0 && max_tiles > 0, "moe_align: empty input");
   TLLM_REQUIRE(n_experts <= 4096, "moe_align: %d experts (at most 4096)", n_experts);
   TLLM_LAUNCH("moe_align", moe_align_kernel, 1, 1024, (size_t)2 * n_experts * sizeof(int), (cudaStream_t)stream, ids, n_pairs,
-              n_experts, tile, max_tiles, sorted_rows, tile_expert);
+              n_experts, tile, max_tiles, sorted_rows, tile_expert, pair_pos);
+  return TLLM_OK;
+}
+
+// in: bfloat16 [rows, k] rows of ld_in values; out: bfloat16 [max_tiles * tile, k], contiguous.
+extern "C" int tllm_moe_gather(const void* in, int ld_in, const int* sorted_rows, const int* tile_expert, int tile,
+                               int max_tiles, int rows_per_input, void* out, int k, void* stream) {
+  TLLM_REQUIRE(k > 0 && k % 8 == 0 && ld_in % 8 == 0 && ((uintptr_t)in & 15) == 0 && ((uintptr_t)out & 15) == 0,
+               "moe_gather: rows of %d values (stride %d) must be multiples of 8 on 16-byte boundaries", k, ld_in);
+  TLLM_REQUIRE(tile > 0 && max_tiles > 0 && rows_per_input > 0, "moe_gather: empty input");
+  TLLM_LAUNCH("moe_gather", moe_gather_kernel, (unsigned)(max_tiles * tile), 128, 0, (cudaStream_t)stream, (const __nv_bfloat16*)in, ld_in,
+              sorted_rows, tile_expert, tile, rows_per_input, (__nv_bfloat16*)out, k);
   return TLLM_OK;
 }
 
@@ -396,11 +428,12 @@ extern "C" int tllm_moe_linear(const void* in, int ld_in, const void* w, const i
 }
 
 extern "C" int tllm_moe_combine(const float* y, const float* weights, int top, const float* shared, const float* logits,
-                                int ld_logits, int gate_col, float* resid, int n_tokens, int width, void* stream) {
+                                int ld_logits, int gate_col, float* resid, int n_tokens, int width, const int* pair_pos,
+                                void* stream) {
   TLLM_REQUIRE(n_tokens > 0 && width > 0 && top > 0, "moe_combine: empty input");
   TLLM_REQUIRE(!shared || logits, "moe_combine: a shared expert needs its gate's logits");
   TLLM_LAUNCH("moe_combine", moe_combine_kernel, (unsigned)n_tokens, width >= 1024 ? 256 : 128, 0, (cudaStream_t)stream, y, weights, top,
-              shared, logits, ld_logits, gate_col, resid, width);
+              shared, logits, ld_logits, gate_col, resid, width, pair_pos);
   return TLLM_OK;
 }
 

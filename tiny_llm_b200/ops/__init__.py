@@ -97,7 +97,7 @@ def replay_tape(tape) -> None:
 def knobs():
     """The module's switches that decide which kernels a step launches; a tape or graph holds for one setting of them."""
     return (force_generic, split_k, cluster_mask, attention_tc, decode_wide_ctas, decode_cluster_merge, qkv_fused_rows,
-            linear_skinny, generic_attention_split, split_mixed_attention, min_gru_segment, linear_attention_segment, moe_mma, moe_wide_tiles, window_attention_tc, attention_maps_tc, attention_maps_decode_pairs, _pdl)
+            linear_skinny, generic_attention_split, split_mixed_attention, min_gru_segment, linear_attention_segment, moe_mma, moe_wide_tiles, moe_tc_rows_per_expert, window_attention_tc, attention_maps_tc, attention_maps_decode_pairs, _pdl)
 
 
 def _i32(t: Optional[torch.Tensor], name: str):
@@ -540,10 +540,15 @@ def moe_max_tiles(pairs: int, num_experts: int, tile: int) -> int:
     return pairs // tile + min(num_experts, pairs)
 
 
-def moe_align(ids: torch.Tensor, num_experts: int, tile: int, sorted_rows: torch.Tensor, tile_expert: torch.Tensor) -> None:
+def moe_align(ids: torch.Tensor, num_experts: int, tile: int, sorted_rows: torch.Tensor, tile_expert: torch.Tensor,
+              pair_pos: Optional[torch.Tensor] = None) -> None:
     """Groups the pairs (token, choice), numbered in the order of `ids`, by expert into tiles of `tile` rows:
-    sorted_rows[tiles * tile] (pair numbers, -1 = padding) and tile_expert[tiles] (-1 = no such tile)."""
-    _need_cuda(ids, sorted_rows, tile_expert)
+    sorted_rows[tiles * tile] (pair numbers, -1 = padding) and tile_expert[tiles] (-1 = no such tile); with `pair_pos`
+    (int32 [pairs]) also where every pair's row lies in that order."""
+    _need_cuda(ids, sorted_rows, tile_expert, pair_pos)
+    _i32(pair_pos, "pair_pos")
+    if pair_pos is not None and pair_pos.numel() != ids.numel():
+        raise KernelError("moe_align: pair_pos does not fit")
     _i32(ids, "ids")
     _i32(sorted_rows, "sorted_rows")
     _i32(tile_expert, "tile_expert")
@@ -551,7 +556,50 @@ def moe_align(ids: torch.Tensor, num_experts: int, tile: int, sorted_rows: torch
     if sorted_rows.numel() != tiles * tile or tiles < moe_max_tiles(ids.numel(), num_experts, tile):
         raise KernelError("moe_align: the tile buffers do not fit")
     lib = build.load_library("moe")
-    _call(lib, lib.tllm_moe_align, _ptr(ids), ids.numel(), num_experts, tile, tiles, _ptr(sorted_rows), _ptr(tile_expert), _stream())
+    _call(lib, lib.tllm_moe_align, _ptr(ids), ids.numel(), num_experts, tile, tiles, _ptr(sorted_rows), _ptr(tile_expert),
+          _ptr(pair_pos), _stream())
+
+
+# Grouped products of prompt portions on tcgen05: at least this many (token, choice) pairs per expert on average
+# (tiles are 128 rows there, so fewer rows would mostly be padding); 0: never
+moe_tc_rows_per_expert = int(os.environ.get("TLLM_MOE_TC_ROWS", "96"))
+MOE_TC_TILE = 128
+
+
+def moe_tc_preferred(pairs: int, num_experts: int, dtype: torch.dtype, *sizes: int) -> bool:
+    """Whether a step's grouped products run on the tcgen05 kernel: bfloat16, enough rows per expert, sizes TMA takes."""
+    return (dtype == torch.bfloat16 and not force_generic and moe_tc_rows_per_expert > 0 and
+            pairs >= moe_tc_rows_per_expert * num_experts and all(x % 8 == 0 for x in sizes))
+
+
+def moe_gather(a: torch.Tensor, sorted_rows: torch.Tensor, tile_expert: torch.Tensor, tile: int, out: torch.Tensor,
+               rows_per_input: int = 1) -> None:
+    """out[p] = a[sorted_rows[p] // rows_per_input] (zeros where sorted_rows is -1; tiles that do not exist are left
+    alone): the grouped order's input rows made contiguous.  bfloat16, rows of a multiple of 8 values."""
+    _need_cuda(a, sorted_rows, tile_expert, out)
+    k = a.shape[1]
+    if a.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or a.stride(1) != 1 or not out.is_contiguous() or \
+            out.shape != (sorted_rows.numel(), k) or sorted_rows.numel() != tile_expert.numel() * tile:
+        raise KernelError("moe_gather: shapes or dtypes do not fit")
+    lib = build.load_library("moe")
+    _call(lib, lib.tllm_moe_gather, _ptr(a), a.stride(0), _ptr(sorted_rows), _ptr(tile_expert), tile, tile_expert.numel(),
+          rows_per_input, _ptr(out), k, _stream())
+
+
+def moe_linear_tc(a: torch.Tensor, w: torch.Tensor, tile_expert: torch.Tensor, out: torch.Tensor, gelu: bool = False) -> None:
+    """The grouped product on tcgen05: a [tiles * 128, K] bfloat16 in the grouped order (every tile of 128 rows one
+    expert's), w [experts, N, K]; out [tiles * 128, N]: bfloat16 of GELU(sums) with gelu=True, else float32 sums."""
+    _need_cuda(a, w, tile_expert, out)
+    _i32(tile_expert, "tile_expert")
+    experts, n, k = w.shape
+    rows = tile_expert.numel() * MOE_TC_TILE
+    if a.shape != (rows, k) or a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or not w.is_contiguous() or \
+            a.stride(1) != 1 or out.shape != (rows, n) or out.stride(1) != 1 or \
+            out.dtype != (torch.bfloat16 if gelu else torch.float32):
+        raise KernelError("moe_linear_tc: shapes or dtypes do not fit")
+    lib = build.load_library("linear_tc")
+    _call(lib, lib.tllm_linear_tc_grouped, _ptr(a), _ptr(w), _ptr(out), rows, n, k, a.stride(0), out.stride(0), experts,
+          _ptr(tile_expert), 10 if gelu else EPI_F32, _ptr(status_word(a.device)), _stream())
 
 
 # bfloat16 grouped products on the tensor cores (0: the FFMA kernel, for comparisons)
@@ -577,19 +625,21 @@ def moe_linear(a: torch.Tensor, w: torch.Tensor, sorted_rows: torch.Tensor, tile
 
 
 def moe_combine(y: torch.Tensor, weights: torch.Tensor, shared: Optional[torch.Tensor], logits: Optional[torch.Tensor],
-                gate_col: int, resid: torch.Tensor) -> None:
+                gate_col: int, resid: torch.Tensor, pair_pos: Optional[torch.Tensor] = None) -> None:
     """resid[t] += sum_c weights[t, c] * y[t * top + c] + sigmoid(logits[t, gate_col]) * shared[t] (the last term only
-    with `shared`); all float32."""
-    _need_cuda(y, weights, shared, logits, resid)
+    with `shared`); all float32.  With `pair_pos` (int32 [T * top]) y is in the grouped order: pair p lies in row pair_pos[p]."""
+    _need_cuda(y, weights, shared, logits, resid, pair_pos)
+    _i32(pair_pos, "pair_pos")
     t, width = resid.shape
     top = weights.shape[1]
-    if y.shape != (t * top, width) or any(x.dtype != torch.float32 or not x.is_contiguous() for x in (y, weights, resid)) or \
+    if (pair_pos is None and y.shape != (t * top, width)) or y.shape[1] != width or \
+            (pair_pos is not None and pair_pos.numel() != t * top) or any(x.dtype != torch.float32 or not x.is_contiguous() for x in (y, weights, resid)) or \
             (shared is not None and (shared.shape != resid.shape or shared.dtype != torch.float32 or not shared.is_contiguous()
                                      or logits is None or logits.dtype != torch.float32 or logits.shape[1] <= gate_col)):
         raise KernelError("moe_combine: shapes or dtypes do not fit")
     lib = build.load_library("moe")
     _call(lib, lib.tllm_moe_combine, _ptr(y), _ptr(weights), top, _ptr(shared), _ptr(logits),
-          0 if logits is None else logits.stride(0), gate_col, _ptr(resid), t, width, _stream())
+          0 if logits is None else logits.stride(0), gate_col, _ptr(resid), t, width, _ptr(pair_pos), _stream())
 
 
 # ----------------------------------------------------------------------------- matrix products

@@ -7,7 +7,9 @@ sigmoid(w_sg . h), one number per token.  act is the exact (erf) GELU.
 
 The experts' matrices are stacked at load ([experts, ff, hidden] and [experts, hidden, ff]); a step sorts its
 (token, choice) pairs by expert into tiles of rows on the device, so that one grouped product serves all experts and
-nothing about the routing reaches the host.  The router's rows and the shared gate's row are one matrix."""
+nothing about the routing reaches the host.  Prompt portions with enough rows per expert copy the grouped rows into
+one contiguous matrix and run both products on the tcgen05 kernel (every tile of 128 rows reads its own expert's rows
+of the stacked weights); smaller steps gather their rows inside an `mma.sync` (bfloat16) or FFMA (float32) kernel.  The router's rows and the shared gate's row are one matrix."""
 from __future__ import annotations
 
 from typing import Optional
@@ -64,16 +66,33 @@ class RoutedExperts:
         ids = ws.get("moe_ids", (t, top), torch.int32)
         weights = ws.get("moe_weights", (t, top), torch.float32)
         ops.moe_route(logits, n, self.correction, self.route_scale, ids, weights)
-        tile = ops.moe_tile_rows(t * top, n, tensor_cores=(ctx.dtype == torch.bfloat16 and self.hidden_size % 8 == 0 and
+        pairs = t * top
+        if ops.moe_tc_preferred(pairs, n, ctx.dtype, self.hidden_size, self.expert_size):
+            # prompt portions: the rows of every expert as whole tiles of 128, made contiguous, through the tcgen05 product
+            tile = ops.MOE_TC_TILE
+            tiles = ops.moe_max_tiles(pairs, n, tile)
+            sorted_rows = ws.get("moe_rows", (tiles * tile,), torch.int32)
+            tile_expert = ws.get("moe_tile_expert", (tiles,), torch.int32)
+            pair_pos = ws.get("moe_pair_pos", (pairs,), torch.int32)
+            ops.moe_align(ids, n, tile, sorted_rows, tile_expert, pair_pos)
+            grouped_in = ws.get("moe_in", (tiles * tile, self.hidden_size), ctx.dtype)
+            ops.moe_gather(h, sorted_rows, tile_expert, tile, grouped_in, rows_per_input=top)
+            act = ws.get("moe_act", (tiles * tile, self.expert_size), ctx.dtype)
+            ops.moe_linear_tc(grouped_in, self.w_up, tile_expert, act, gelu=True)
+            y = ws.get("moe_y", (tiles * tile, self.hidden_size), torch.float32)
+            ops.moe_linear_tc(act, self.w_down, tile_expert, y)
+        else:
+            pair_pos = None
+            tile = ops.moe_tile_rows(pairs, n, tensor_cores=(ctx.dtype == torch.bfloat16 and self.hidden_size % 8 == 0 and
                                                              self.expert_size % 8 == 0))
-        tiles = ops.moe_max_tiles(t * top, n, tile)
-        sorted_rows = ws.get("moe_rows", (tiles * tile,), torch.int32)
-        tile_expert = ws.get("moe_tile_expert", (tiles,), torch.int32)
-        ops.moe_align(ids, n, tile, sorted_rows, tile_expert)
-        act = ws.get("moe_act", (t * top, self.expert_size), ctx.dtype)
-        ops.moe_linear(h, self.w_up, sorted_rows, tile_expert, tile, act, rows_per_input=top, gelu=True)
-        y = ws.get("moe_y", (t * top, self.hidden_size), torch.float32)
-        ops.moe_linear(act, self.w_down, sorted_rows, tile_expert, tile, y, rows_per_input=1, gelu=False)
+            tiles = ops.moe_max_tiles(pairs, n, tile)
+            sorted_rows = ws.get("moe_rows", (tiles * tile,), torch.int32)
+            tile_expert = ws.get("moe_tile_expert", (tiles,), torch.int32)
+            ops.moe_align(ids, n, tile, sorted_rows, tile_expert)
+            act = ws.get("moe_act", (pairs, self.expert_size), ctx.dtype)
+            ops.moe_linear(h, self.w_up, sorted_rows, tile_expert, tile, act, rows_per_input=top, gelu=True)
+            y = ws.get("moe_y", (pairs, self.hidden_size), torch.float32)
+            ops.moe_linear(act, self.w_down, sorted_rows, tile_expert, tile, y, rows_per_input=1, gelu=False)
         shared = None
         if self.shared_size is not None:
             sact = ws.get("ffn_act", (t, self.shared_size), ctx.dtype)
@@ -81,7 +100,7 @@ class RoutedExperts:
             ops.gelu(sact, sact)
             shared = ws.get("moe_shared", (t, self.hidden_size), torch.float32)
             ops.linear(sact, self.w_shared_down, shared)
-        ops.moe_combine(y, weights, shared, logits, n, resid)
+        ops.moe_combine(y, weights, shared, logits, n, resid, pair_pos)
 
 
 register_part("ffn", "routed_experts", RoutedExperts)
