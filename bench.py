@@ -688,6 +688,22 @@ def zozenex_kernels(dtype, device, pk, tokens=2048):
          2.0 * t * top * ff * width)
     flop("moe_linear down", time_kernel(lambda: ops.moe_linear(act, w_down, rows, texp, tile, yexp, rows_per_input=1), flush, repeats=5),
          2.0 * t * top * ff * width)
+    if dtype == torch.bfloat16:
+        # what prompt portions run: the grouped order made contiguous, both products on tcgen05 (tiles of 128 rows)
+        t128 = ops.moe_max_tiles(t * top, experts, ops.MOE_TC_TILE)
+        rows128 = torch.empty(t128 * 128, dtype=torch.int32, device=device)
+        texp128 = torch.empty(t128, dtype=torch.int32, device=device)
+        pos128 = torch.empty(t * top, dtype=torch.int32, device=device)
+        ops.moe_align(ids, experts, 128, rows128, texp128, pos128)
+        gin = torch.zeros(t128 * 128, width, dtype=dtype, device=device)
+        gact = torch.zeros(t128 * 128, ff, dtype=dtype, device=device)
+        gy = torch.zeros(t128 * 128, width, device=device)
+        mem("moe_gather", time_kernel(lambda: ops.moe_gather(h_in, rows128, texp128, 128, gin, rows_per_input=top), flush),
+            t * top * width * 2 * isz)
+        flop("moe_linear_tc up + gelu (tcgen05)", time_kernel(lambda: ops.moe_linear_tc(gin, w_up, texp128, gact, gelu=True), flush),
+             2.0 * t * top * ff * width)
+        flop("moe_linear_tc down (tcgen05)", time_kernel(lambda: ops.moe_linear_tc(gact, w_down, texp128, gy), flush),
+             2.0 * t * top * ff * width)
     dense_in = torch.randn(t * top, width, device=device).to(dtype)
     flop("linear of as many rows (like)", time_kernel(lambda: ops.linear(dense_in, w_up[0], act), flush), 2.0 * t * top * ff * width)
     shared = torch.randn(t, width, device=device)
