@@ -32,7 +32,7 @@ def test_linear_attention_scan_from_a_state_for_unequal_requests(dtype, segment,
     from tiny_llm_b200.engine import Workspace
     monkeypatch.setattr(ops, "linear_attention_segment", segment)
     g = torch.Generator().manual_seed(2)
-    lens, slots = [1, 23, 2, 40, 9], [4, 0, 5, 2, 1]
+    lens, slots = [1, 23, 2, 70, 9], [4, 0, 5, 2, 1]      # the longest is long enough for segments
     batch, cu = scan_batch(lens, slots)
     t = cu[-1]
     # one projection buffer with q, k, v as column slices, as the mixer hands them over

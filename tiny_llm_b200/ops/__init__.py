@@ -314,8 +314,9 @@ def rms_norm_add(x: torch.Tensor, weight: torch.Tensor, eps: float, scale: float
           ctypes.c_float(scale), 1 if clear else 0, _stream())
 
 
-# Portions of at least twice this many tokens run the linear-attention recurrence in segments (bfloat16 only: the
-# 32-bit path always walks a request's tokens in order, so that its state has the same bits however it was cut); 0: never.
+# Portions of at least 64 tokens run the linear-attention recurrence in segments of at most this many tokens (bfloat16
+# only: the 32-bit path always walks a request's tokens in order, so that its state has the same bits however it was
+# cut); 0: never.
 linear_attention_segment = int(os.environ.get("TLLM_LINEAR_ATTENTION_SEGMENT", "128"))
 
 
@@ -343,9 +344,10 @@ def linear_attention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, hea
                              gate_bias.dtype != torch.float32 or gate_bias.numel() != heads * key_dim):
         raise KernelError("linear_attention_scan: the gate and its bias do not fit")
     seg, summary = 0, None
-    if q.dtype == torch.bfloat16 and workspace is not None and linear_attention_segment > 0 and \
-            batch.max_q_len >= 2 * linear_attention_segment:
-        seg = linear_attention_segment
+    if q.dtype == torch.bfloat16 and workspace is not None and linear_attention_segment > 0 and batch.max_q_len >= 64:
+        # shorter portions are cut finer, so that there are segments enough to fill the SMs: a sixteenth of the longest
+        # portion, at least 32 tokens, at most the switch's value
+        seg = min(linear_attention_segment, max(32, (batch.max_q_len // 16) // 8 * 8))
         segs = -(-batch.max_q_len // seg)
         per = heads * (key_dim * value_dim + key_dim)
         summary = workspace.get("lin_attn_summary", (batch.num_requests * segs * per,), torch.float32)
@@ -562,7 +564,7 @@ def moe_align(ids: torch.Tensor, num_experts: int, tile: int, sorted_rows: torch
 
 # Grouped products of prompt portions on tcgen05: at least this many (token, choice) pairs per expert on average
 # (tiles are 128 rows there, so fewer rows would mostly be padding); 0: never
-moe_tc_rows_per_expert = int(os.environ.get("TLLM_MOE_TC_ROWS", "96"))
+moe_tc_rows_per_expert = int(os.environ.get("TLLM_MOE_TC_ROWS", "32"))
 MOE_TC_TILE = 128
 
 
