@@ -221,6 +221,8 @@ def test_window_and_block_attention_finds_the_planted_keys(dtype, tc, size, pool
         same = pz.window_pool_sum(q.double(), k.double(), v.double(), scale, cap, pb.double(), size, pool)
         assert float((other - same).abs().max()) > 0.3
 
+    from tiny_llm_b200.engine import Workspace
+    ws = Workspace(torch.device(DEV))      # decoded tokens walk their keys in several runs that add into a buffer of it
     pages_needed = 2 * sum(-(-n // page) for n in lens) + 4
     kc = torch.full((pages_needed, kvh, page, kd), float("nan"), dtype=dtype, device=DEV)
     vc = torch.full((pages_needed, kvh, page, vd), float("nan"), dtype=dtype, device=DEV)
@@ -248,13 +250,14 @@ def test_window_and_block_attention_finds_the_planted_keys(dtype, tc, size, pool
         for n in new:
             cu.append(cu[-1] + n)
         batch = SimpleNamespace(positions=i32(posl), token_request=i32(reql), num_tokens=len(posl), cu_q=i32(cu),
-                                q_start=i32(before), num_requests=len(new), max_q_len=max(new))
+                                q_start=i32(before), num_requests=len(new), max_q_len=max(new),
+                                max_kv_len=max(b + n for b, n in zip(before, new)))
         ops.rope_halves_kv_write(qkv, batch.positions, None, 0, fv, heads, kvh, kvh, kd, vd, kc, vc, i32(slots))
         if pool:
             ops.pool_kv_blocks(kc, vc, table, pkc, pvc, i32(pslots), batch, pool)
         out = torch.empty(len(posl), heads * vd, dtype=dtype, device=DEV)
         ops.window_pool_attention(qkv, heads, kvh, kd, vd, kc, vc, table, pkc if pool else None, pvc if pool else None,
-                                  ptable, batch, out, scale, cap, pb.to(DEV), size, pool, fv)
+                                  ptable, batch, out, scale, cap, pb.to(DEV), size, pool, fv, workspace=ws)
         o = out.cpu().double().view(-1, heads, vd)
         for row, (p, x) in enumerate(zip(posl, reql)):
             got[x][p] = o[row]

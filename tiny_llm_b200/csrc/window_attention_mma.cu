@@ -58,8 +58,12 @@ __device__ __forceinline__ void split2(float p0, float p1, unsigned& hi, unsigne
   lo = pack_bf16(p0 - __bfloat162float(h0), p1 - __bfloat162float(h1));
 }
 
+// splits > 1 (few rows, many keys: decoded tokens): blockIdx.x also names one of `splits` runs of the key tiles; every
+// run adds its part of the sums into the zeroed float32 buffer `acc` [tokens, heads * VD] (the weights are not
+// normalised over the keys, so parts simply add), and window_attention_finish_kernel turns the sums back and stores them.
 __global__ void __launch_bounds__(NTHREADS) window_pool_attention_mma_kernel(WinArgs a, const int* __restrict__ cu_q,
-                                                                             const int* __restrict__ q_start) {
+                                                                             const int* __restrict__ q_start, int splits,
+                                                                             float* __restrict__ acc) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [BM][LDK]
   __nv_bfloat16* sK = sQ + BM * LDK;                                // [2][BN][LDK]
@@ -72,7 +76,8 @@ __global__ void __launch_bounds__(NTHREADS) window_pool_attention_mma_kernel(Win
   pdl_wait();
   const int q0 = cu_q[r], qn = cu_q[r + 1] - q0, start = q_start[r];
   const int TPT = BM / G;                      // whole tokens per tile: row m is (token m / G, head m % G), m < TPT * G
-  const int tok_lo = blockIdx.x * TPT;
+  const int tok_lo = (blockIdx.x / splits) * TPT;
+  const int split = blockIdx.x % splits;
   if (tok_lo >= qn) return;
   const int tok_hi = min(qn - 1, tok_lo + TPT - 1);
   const int i_min = start + tok_lo, i_max = start + tok_hi;
@@ -80,7 +85,10 @@ __global__ void __launch_bounds__(NTHREADS) window_pool_attention_mma_kernel(Win
   const int nblk = (W > 0 && P > 0 && i_max - W - P + 1 >= 0) ? (i_max - W - P + 1) / P + 1 : 0;
   const int lo = W > 0 ? max(0, i_min - W + 1) : 0;
   const int total = nblk + (i_max - lo + 1);
-  const int ntiles = (total + BN - 1) / BN;
+  const int all_tiles = (total + BN - 1) / BN;
+  const int per_split = (all_tiles + splits - 1) / splits;
+  const int kt0 = split * per_split, ntiles = min(all_tiles, kt0 + per_split);   // this CTA's tiles: [kt0, ntiles)
+  if (kt0 >= ntiles) return;
   const int* table = a.table + (size_t)r * a.max_blocks;
   const int* ptable = a.ptable ? a.ptable + (size_t)r * a.pmax_blocks : nullptr;
   const __nv_bfloat16* qkv = (const __nv_bfloat16*)a.qkv;
@@ -124,7 +132,7 @@ __global__ void __launch_bounds__(NTHREADS) window_pool_attention_mma_kernel(Win
     for (int c = part * 8; c < VD; c += 32) cp_async16(vd_ + c, vsrc + (ok ? c : 0), ok);
     if (part == 0) sCode[stage * BN + n] = code;
   };
-  load_tile(0, 0);
+  load_tile(kt0, 0);
   asm volatile("cp.async.commit_group;");
 
   // this thread's two rows: (token, head), position and bias
@@ -140,13 +148,13 @@ __global__ void __launch_bounds__(NTHREADS) window_pool_attention_mma_kernel(Win
 #pragma unroll
   for (int x = 0; x < VD / 8; ++x) o[x][0] = o[x][1] = o[x][2] = o[x][3] = 0.f;
 
-  for (int kt = 0; kt < ntiles; ++kt) {
-    const int stage = kt & 1;
+  for (int kt = kt0; kt < ntiles; ++kt) {
+    const int stage = (kt - kt0) & 1;
     if (kt + 1 < ntiles) load_tile(kt + 1, stage ^ 1);
     asm volatile("cp.async.commit_group;");
     asm volatile("cp.async.wait_group 1;");
     __syncthreads();
-    if (kt == 0) {
+    if (kt == kt0) {
 #pragma unroll
       for (int kk = 0; kk < KD / 16; ++kk)
         ldsm4(qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3], sQ + (warp * 16 + (lane & 15)) * LDK + kk * 16 + (lane >> 4) * 8);
@@ -210,6 +218,16 @@ __global__ void __launch_bounds__(NTHREADS) window_pool_attention_mma_kernel(Win
     if (!(half ? okB : okA)) continue;
     const int row = half ? rB : rA, i = half ? iB : iA, h = half ? hB : hA;
     __nv_bfloat16* dst = out + (size_t)(q0 + tok_lo + row / G) * a.nh * VD + (size_t)h * VD;
+    if (splits > 1) {
+      float* part = acc + (size_t)(q0 + tok_lo + row / G) * a.nh * VD + (size_t)h * VD;
+#pragma unroll
+      for (int x = 0; x < VD / 8; ++x) {
+        const int m = x * 8 + (lane & 3) * 2;
+        atomicAdd(part + m, o[x][half * 2]);
+        atomicAdd(part + m + 1, o[x][half * 2 + 1]);
+      }
+      continue;
+    }
     if (a.fv) {
       const float pos = (float)i;
 #pragma unroll
@@ -233,12 +251,43 @@ __global__ void __launch_bounds__(NTHREADS) window_pool_attention_mma_kernel(Win
   }
 }
 
+// One warp per (token, head): the sums of the key runs, turned back by the token's position (when values are rotated),
+// stored in bfloat16; the buffer is handed back zeroed.
+__global__ void window_attention_finish_kernel(float* __restrict__ acc, const int* __restrict__ positions,
+                                               const float* __restrict__ fv, __nv_bfloat16* __restrict__ out, int nh,
+                                               long long n_rows) {
+  pdl_trigger();
+  pdl_wait();
+  const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= n_rows) return;
+  const int lane = threadIdx.x & 31;
+  float* src = acc + row * VD;
+  __nv_bfloat16* dst = out + row * VD;
+  const float pos = (float)positions[row / nh];
+  for (int m = lane; m < VD / 2; m += 32) {
+    const float u = src[m], v = src[m + VD / 2];
+    src[m] = 0.f;
+    src[m + VD / 2] = 0.f;
+    if (fv) {
+      float sn, cs;
+      sincosf(__fmul_rn(pos, fv[m]), &sn, &cs);
+      dst[m] = __float2bfloat16_rn(fmaf(u, cs, __fmul_rn(v, sn)));
+      dst[m + VD / 2] = __float2bfloat16_rn(fmaf(v, cs, -__fmul_rn(u, sn)));
+    } else {
+      dst[m] = __float2bfloat16_rn(u);
+      dst[m + VD / 2] = __float2bfloat16_rn(v);
+    }
+  }
+}
+
 }  // namespace tllm
 
 using namespace tllm;
 
+// splits > 1: the key tiles of every row tile in that many runs, summed through `acc` (float32 [tokens, heads * VD],
+// zeroed; handed back zeroed).
 extern "C" int tllm_window_pool_attention_mma(const WinArgs* args, const int* cu_q, const int* q_start, int n_requests,
-                                              int max_q_len, void* stream) {
+                                              int max_q_len, int splits, float* acc, void* stream) {
   const WinArgs& a = *args;
   TLLM_REQUIRE(a.kd == KD && a.vd == VD, "window_pool_attention_mma: built for keys of %d and values of %d, not %d and %d", KD, VD, a.kd, a.vd);
   TLLM_REQUIRE(a.n_tokens > 0 && n_requests > 0 && max_q_len > 0 && a.nh > 0 && a.nkv > 0 && a.nh % a.nkv == 0, "window_pool_attention_mma: sizes do not fit");
@@ -255,7 +304,13 @@ extern "C" int tllm_window_pool_attention_mma(const WinArgs* args, const int* cu
     configured = true;
   }
   const int tokens_per_tile = BM / G;
-  const dim3 grid((unsigned)((max_q_len + tokens_per_tile - 1) / tokens_per_tile), (unsigned)a.nkv, (unsigned)n_requests);
-  TLLM_LAUNCH("window_pool_attention_mma", window_pool_attention_mma_kernel, grid, NTHREADS, smem, (cudaStream_t)stream, a, cu_q, q_start);
+  TLLM_REQUIRE(splits >= 1 && (splits == 1 || acc != nullptr), "window_pool_attention_mma: key runs need a float32 buffer");
+  const dim3 grid((unsigned)((max_q_len + tokens_per_tile - 1) / tokens_per_tile * splits), (unsigned)a.nkv, (unsigned)n_requests);
+  TLLM_LAUNCH("window_pool_attention_mma", window_pool_attention_mma_kernel, grid, NTHREADS, smem, (cudaStream_t)stream, a, cu_q, q_start, splits, acc);
+  if (splits > 1) {
+    const long long n_rows = (long long)a.n_tokens * a.nh;
+    TLLM_LAUNCH("window_attention_finish", window_attention_finish_kernel, (unsigned)((n_rows + 3) / 4), 128, 0, (cudaStream_t)stream,
+                acc, a.positions, a.fv, (__nv_bfloat16*)a.out, a.nh, n_rows);
+  }
   return TLLM_OK;
 }

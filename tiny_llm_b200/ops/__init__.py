@@ -97,7 +97,7 @@ def replay_tape(tape) -> None:
 def knobs():
     """The module's switches that decide which kernels a step launches; a tape or graph holds for one setting of them."""
     return (force_generic, split_k, cluster_mask, attention_tc, decode_wide_ctas, decode_cluster_merge, qkv_fused_rows,
-            linear_skinny, generic_attention_split, split_mixed_attention, min_gru_segment, linear_attention_segment, moe_mma, moe_wide_tiles, moe_tc_rows_per_expert, window_attention_tc, attention_maps_tc, attention_maps_decode_pairs, _pdl)
+            linear_skinny, generic_attention_split, split_mixed_attention, min_gru_segment, linear_attention_segment, moe_mma, moe_wide_tiles, moe_tc_rows_per_expert, window_attention_tc, window_attention_splits, attention_maps_tc, attention_maps_decode_pairs, _pdl)
 
 
 def _i32(t: Optional[torch.Tensor], name: str):
@@ -442,6 +442,8 @@ class _WinArgs(ctypes.Structure):
 
 # bfloat16 window attention on the tensor cores (0: the CUDA-core kernel, for comparisons)
 window_attention_tc = os.environ.get("TLLM_WINDOW_ATTENTION_TC", "1") != "0"
+# ... and its key tiles in several runs per row tile when the grid would not fill the SMs (decoded tokens); 0: one run
+window_attention_splits = os.environ.get("TLLM_WINDOW_ATTENTION_SPLITS", "1") != "0"
 
 
 def _keep(struct):
@@ -455,7 +457,7 @@ def window_pool_attention(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, 
                           pool_k: Optional[torch.Tensor], pool_v: Optional[torch.Tensor],
                           pool_table: Optional[torch.Tensor], batch, out: torch.Tensor, scale: float,
                           softcap: Optional[float], head_bias: torch.Tensor, window: Optional[int], pool: Optional[int],
-                          freq_v: Optional[torch.Tensor]) -> None:
+                          freq_v: Optional[torch.Tensor], workspace=None) -> None:
     """Attention without softmax: out[t, h] = sum over visible keys of sigmoid(cap(q . k * scale) + head_bias[h]) * v,
     cap(s) = softcap * tanh(s / softcap) (None: s).  Visible to position i: tokens j with 0 <= i - j < window (None:
     all j <= i) and, with `pool`, the block rows b of pool_k / pool_v with b * pool + pool - 1 <= i - window.  With
@@ -497,8 +499,19 @@ def window_pool_attention(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, 
             qkv.data_ptr() % 16 == 0 and getattr(batch, "cu_q", None) is not None:
         # bfloat16: the tensor-core kernel compiled for this pair of sizes (prompt portions and decoded tokens alike)
         lib = build.load_library("window_attention_mma", flags=(f"-DTLLM_HEAD_DIM={key_dim}", f"-DTLLM_VALUE_DIM={value_dim}"))
+        # few CTAs and many keys (decoded tokens): the key tiles of a row tile in runs that add into a 32-bit buffer
+        splits, acc = 1, None
+        max_kv = getattr(batch, "max_kv_len", 0)
+        if workspace is not None and window_attention_splits and max_kv:
+            tokens_per_tile = 64 // heads_per_kv
+            ctas = -(-batch.max_q_len // tokens_per_tile) * num_kv_heads * batch.num_requests
+            keys = (min(max_kv, window) if window else max_kv) + (max_kv // pool if pool else 0)
+            tiles = -(-keys // 32)
+            splits = max(1, min(16, sm_count(qkv.device) // ctas, tiles // 4))
+            if splits > 1:
+                acc = workspace.get_zeroed("window_attn_acc", (t, num_heads * value_dim))
         _call(lib, lib.tllm_window_pool_attention_mma, _keep(a), _ptr(batch.cu_q), _ptr(batch.q_start), batch.num_requests,
-              batch.max_q_len, _stream())
+              batch.max_q_len, splits, _ptr(acc), _stream())
         return
     lib = build.load_library("window_attention")
     _call(lib, lib.tllm_window_pool_attention, _keep(a), _code(qkv.dtype), _stream())

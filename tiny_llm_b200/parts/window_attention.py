@@ -98,7 +98,7 @@ class PooledWindowAttention:
         ops.window_pool_attention(qkv, nh, nkv, kd, vd, tokens.k, tokens.v, tokens.block_table,
                                   None if blocks is None else blocks.k, None if blocks is None else blocks.v,
                                   None if blocks is None else blocks.block_table, ctx.batch, out, self.scale,
-                                  self.softcap, self.head_bias, self.window, self.pool, self.freq_v)
+                                  self.softcap, self.head_bias, self.window, self.pool, self.freq_v, workspace=ctx.workspace)
         ops.linear(out, self.w_o, resid, accumulate=True)
 
 
